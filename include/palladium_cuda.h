@@ -1,0 +1,207 @@
+/* palladium_cuda.h -- C ABI of libpalladium_cuda.so, the CUDA (sm_100a) handler
+ * that takes the place of the reference's only native component, the XLA-FFI
+ * handler `palladium_dispatch` (native/ffi/palladium_ffi.cpp:110-209).
+ *
+ * The reference handler receives MSL source + entry-point name + grid +
+ * threadgroup + math_mode as attributes and a list of argument / result
+ * buffers.  Here the kernels are fixed, hand-written CUDA families, so the
+ * `msl_source` / `function_name` pair is replaced by a family id and a small
+ * parameter struct; everything else (grid, threadgroup, math_mode ordinal,
+ * "remaining args" / "remaining rets" as pointer arrays) keeps its meaning.
+ *
+ * All entry points are plain C: pointers, sizes, ints.  No entry point takes
+ * ownership of a caller buffer.  Every function that can fail returns a
+ * pd_status and, when `err` is non-NULL, copies a NUL-terminated message into
+ * the caller's buffer (the reference returns a malloc'ed message that must be
+ * freed with mr_free_error_message, palladium_ffi.cpp:55-63; copying into the
+ * caller's buffer avoids a cross-library free).
+ */
+#ifndef PALLADIUM_CUDA_H_
+#define PALLADIUM_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PD_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define PD_API __attribute__((visibility("default")))
+#else
+#define PD_API
+#endif
+
+typedef enum pd_status {
+    PD_OK = 0,
+    PD_ERR_INVALID_ARGUMENT = 1, /* maps to xla::ffi::Error::InvalidArgument (palladium_ffi.cpp:118-121) */
+    PD_ERR_INTERNAL = 2,         /* maps to xla::ffi::Error::Internal (palladium_ffi.cpp:126,139,147,167) */
+    PD_ERR_CUDA = 3,             /* a CUDA runtime call failed; message carries cudaGetErrorString */
+    PD_ERR_DEVICE_STATUS = 4     /* a kernel reported a non-zero device status word */
+} pd_status;
+
+/* MRMathMode ordinals as the reference passes them (src/palladium/ffi.py:38;
+ * range check at native/ffi/palladium_ffi.cpp:118-121). */
+typedef enum pd_math_mode {
+    PD_MATH_SAFE = 0,    /* IEEE op order, no FMA contraction, IEEE div/sqrt, no flush-to-zero */
+    PD_MATH_RELAXED = 1, /* FMA contraction allowed, accurate div/sqrt/libm */
+    PD_MATH_FAST = 2     /* reassociation + approximate transcendentals + flush-to-zero */
+} pd_math_mode;
+
+/* Kernel families: one per reference kernel on the integrator path. */
+typedef enum pd_family {
+    PD_FAMILY_LV_RK4 = 0,        /* lv_kernel, examples/01_ode_ensembles.py:72-91 */
+    PD_FAMILY_VDP_BS32 = 1,      /* vdp_adaptive_kernel, examples/02_adaptive_lockstep.py:69-171 */
+    PD_FAMILY_GBM_THREEFRY = 2,  /* pallas_gbm_kernel, examples/03_sde_montecarlo.py:97-119 */
+    PD_FAMILY_GRAY_SCOTT = 3,    /* gray_scott_kernel + stepping loop, examples/04_reaction_diffusion.py:61-109 */
+    PD_FAMILY_LV_RK4_DF32 = 4,   /* lv_rk4_df32, examples/05_df32_precision.py:27-80 */
+    PD_FAMILY_KEPLER_RK4_DF32 = 5, /* same df32 RK4 scheme on the two-body problem */
+    PD_FAMILY_THREEFRY_BITS = 6, /* random_bits / uniform / fold_in, src/palladium/emit/rules.py:168-201 */
+    PD_FAMILY_COUNT = 7
+} pd_family;
+
+/* ---- per-family parameter blocks (passed by pointer + sizeof) ------------ */
+
+/* in:  x0,y0,a,b,c,d  (N) f32.   out: x,y (N) f32.
+ * The three step constants are rounded to f32 from double products exactly as
+ * Python folds them: f32(0.5*dt), f32(dt), f32(dt/6). */
+typedef struct pd_lv_rk4_params {
+    double dt;
+    int64_t steps;
+} pd_lv_rk4_params;
+
+/* in:  x0,v0,mu (N) f32.
+ * out_layout 0: t,x,v,steps,rejected,real  (6 x (N) f32)   examples/02:173-181
+ * out_layout 1: t,x,v,steps,rejected       (5 x (N) f32)   tests/test_08_adaptive.py:33-142
+ * out_layout 2: state (N,2) f32, accepted (N) i32, rejected (N) i32
+ *               (accepted == the reference's `real` counter). */
+typedef struct pd_vdp_bs32_params {
+    double t1, rtol, atol, dt0;
+    double pcoeff, icoeff, safety, factor_min, factor_max;
+    int64_t error_order;
+    int64_t max_steps;
+    int64_t out_layout;
+} pd_vdp_bs32_params;
+
+/* in:  key data (2) u32.   out[0]: (N) f32 payoff (output_kind 0) or terminal
+ * price (output_kind 1); optional out[1]: (2) f64 = {sum payoff, sum payoff^2}
+ * over this call's paths.  Path i uses RNG stream fold_in(key, path_offset+i). */
+typedef struct pd_gbm_params {
+    double s0, strike, r, sigma, t;
+    int64_t steps;
+    int64_t path_offset;
+    int64_t output_kind;
+} pd_gbm_params;
+
+/* in:  u,v (rows_alloc, cols) f32 row-major.   out: u,v same shape.
+ * halo == 0: rows_alloc == rows, periodic in both directions (the reference).
+ * halo  > 0: a row slab with `halo` ghost rows above and below
+ *            (rows_alloc == rows + 2*halo), periodic in columns only; step s
+ *            (1-based, steps <= halo) updates rows [s, rows_alloc - s). */
+typedef struct pd_gray_scott_params {
+    double du, dv, f, k, dt;
+    int64_t steps;
+    int64_t rows, cols;
+    int64_t halo;
+} pd_gray_scott_params;
+
+/* in:  x0,y0,a,b,c,d (N) f32.   out: x,y (N) f32 (df32 state rounded to f32).
+ * dt is rounded to f32 first, as the reference passes a float scalar. */
+typedef struct pd_lv_rk4_df32_params {
+    double dt;
+    int64_t steps;
+} pd_lv_rk4_df32_params;
+
+/* in:  x,y,vx,vy each as (hi, lo): 8 x (N) f32.   out: same 8 arrays.
+ * dt and gm are split into df32 (hi, lo) from the doubles given here. */
+typedef struct pd_kepler_rk4_df32_params {
+    double dt, gm;
+    int64_t steps;
+} pd_kepler_rk4_df32_params;
+
+/* in:  key data (2) u32 [, data (M) u32 for op 2].
+ * op 0: out (N) u32 = random_bits(key, (N,))
+ * op 1: out (N) f32 = uniform(key, (N,))
+ * op 2: out (M,2) u32 = key_data(fold_in(key, data[m]))
+ * op 3: out (G,count) f32, row g = uniform(fold_in(key, g), (count,)) */
+typedef struct pd_threefry_params {
+    int64_t op;
+    int64_t count;
+} pd_threefry_params;
+
+/* ---- launch geometry report (the `.explain()` payload) -------------------- */
+typedef struct pd_launch_info {
+    char kernel_name[64];
+    int64_t cuda_grid[3];
+    int64_t cuda_block[3];
+    int64_t items_per_thread;
+    int64_t launches;          /* kernel launches one call performs */
+    int64_t scratch_bytes;     /* device scratch the call needs beyond in/out */
+    int32_t regs_per_thread;   /* -1 when no CUDA device is present */
+    int32_t static_smem_bytes; /* -1 when no CUDA device is present */
+    int32_t dynamic_smem_bytes;
+    int32_t blocks_per_sm;     /* occupancy; -1 when no CUDA device is present */
+} pd_launch_info;
+
+/* ABI version of the loaded library (== PD_ABI_VERSION it was built with). */
+PD_API int pd_version(void);
+
+/* Number of CUDA devices visible, or 0 (never fails). */
+PD_API int pd_device_count(void);
+
+/* Launch one call of a family on DEVICE buffers, stream-ordered, no host
+ * synchronisation.  Replaces the dispatch half of PalladiumDispatch
+ * (palladium_ffi.cpp:150-165) for callers that already hold device memory.
+ *   grid / block: the reference's grid (padded to 3 dims, ffi.py:167-169) and
+ *   threadgroup (0,0,0 = library chooses, palladium_ffi.cpp:158-162).
+ *   workspace: optional caller-provided device scratch of at least
+ *   pd_launch_info.scratch_bytes; NULL lets the library use its cached pool. */
+PD_API int pd_launch(int family, const void* params, size_t params_bytes, int math_mode,
+              const int64_t grid[3], const int64_t block[3],
+              int n_in, const void* const* in, const size_t* in_bytes,
+              int n_out, void* const* out, const size_t* out_bytes,
+              void* workspace, size_t workspace_bytes,
+              void* cuda_stream, char* err, size_t err_cap);
+
+/* Same call on HOST buffers: uploads the inputs, launches, downloads the
+ * outputs and returns when they are in place -- the contract of the reference
+ * handler, which is registered on XLA's "cpu" platform and blocks until the
+ * outputs are flushed (src/palladium/ffi.py:78; palladium_ffi.cpp:165-188).
+ * Thread-safe; device staging buffers come from a per-thread cached pool. */
+PD_API int pd_dispatch_host(int family, const void* params, size_t params_bytes, int math_mode,
+                     const int64_t grid[3], const int64_t block[3],
+                     int n_in, const void* const* in, const size_t* in_bytes,
+                     int n_out, void* const* out, const size_t* out_bytes,
+                     char* err, size_t err_cap);
+
+/* Launch geometry for a call, without launching anything (the native half of
+ * MetalCallable.explain, src/palladium/__init__.py:116-128).  Works without a
+ * GPU; the register / shared-memory / occupancy fields are then -1. */
+PD_API int pd_explain(int family, const void* params, size_t params_bytes, int math_mode,
+               const int64_t grid[3], const int64_t block[3],
+               pd_launch_info* info, char* err, size_t err_cap);
+
+/* Tuning knobs for experiments (e.g. "lv_items_per_thread", "vdp_variant").
+ * Returns PD_ERR_INVALID_ARGUMENT for an unknown key. */
+PD_API int pd_set_tuning(const char* key, int64_t value);
+PD_API int pd_get_tuning(const char* key, int64_t* value);
+
+/* Roofline denominators measured on the current device: a chain of dependent
+ * FP32 FMAs (2 flops each) and a chain of 32-bit integer add/xor/funnel-shift
+ * operations, both with enough independent chains per thread to saturate issue.
+ * Results in operations per second.  Time is taken with CUDA events. */
+PD_API int pd_measure_fp32_fma_peak(double* flops_per_s, char* err, size_t err_cap);
+PD_API int pd_measure_int32_alu_peak(double* ops_per_s, char* err, size_t err_cap);
+
+/* Milliseconds the kernels of the most recent pd_launch / pd_dispatch_host
+ * call of the calling thread took on the device (CUDA events on the launch
+ * stream), or a negative value if timing was not enabled.  Enable with
+ * pd_set_tuning("time_kernels", 1); it adds an event pair and a synchronise. */
+PD_API double pd_last_kernel_ms(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PALLADIUM_CUDA_H_ */

@@ -1,0 +1,276 @@
+"""ctypes binding of libpalladium_cuda.so (declared in include/palladium_cuda.h).
+
+This is the Python half of the drop-in boundary: the reference loads its native
+handler with `ctypes.CDLL` and hands it to XLA (src/palladium/ffi.py:64-79);
+here the same library is loaded the same way and its C entry points are called
+directly.  `PALLADIUM_FFI_LIBRARY` overrides the path, as in the reference
+(src/palladium/ffi.py:42).
+
+There is no fallback: if the library is missing, every call raises EmitError
+with the build command.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+from .errors import DispatchError, EmitError, PalladiumError
+
+__all__ = [
+    "library",
+    "library_path",
+    "LvRk4Params",
+    "VdpBs32Params",
+    "GbmParams",
+    "GrayScottParams",
+    "LvRk4Df32Params",
+    "KeplerRk4Df32Params",
+    "ThreefryParams",
+    "LaunchInfo",
+    "EXPORTED_SYMBOLS",
+    "FAMILY_IDS",
+]
+
+_LIBRARY_NAME = "libpalladium_cuda.so"
+PD_ABI_VERSION = 1
+
+EXPORTED_SYMBOLS = (
+    "pd_version",
+    "pd_device_count",
+    "pd_launch",
+    "pd_dispatch_host",
+    "pd_explain",
+    "pd_set_tuning",
+    "pd_get_tuning",
+    "pd_measure_fp32_fma_peak",
+    "pd_measure_int32_alu_peak",
+    "pd_last_kernel_ms",
+)
+
+FAMILY_IDS = {
+    "lv_rk4": 0,
+    "vdp_bs32": 1,
+    "gbm_threefry": 2,
+    "gray_scott": 3,
+    "lv_rk4_df32": 4,
+    "kepler_rk4_df32": 5,
+    "threefry_bits": 6,
+}
+
+_i64 = ctypes.c_int64
+_dbl = ctypes.c_double
+
+
+class LvRk4Params(ctypes.Structure):
+    _fields_ = [("dt", _dbl), ("steps", _i64)]
+
+
+class VdpBs32Params(ctypes.Structure):
+    _fields_ = [("t1", _dbl), ("rtol", _dbl), ("atol", _dbl), ("dt0", _dbl), ("pcoeff", _dbl), ("icoeff", _dbl),
+                ("safety", _dbl), ("factor_min", _dbl), ("factor_max", _dbl), ("error_order", _i64),
+                ("max_steps", _i64), ("out_layout", _i64)]
+
+
+class GbmParams(ctypes.Structure):
+    _fields_ = [("s0", _dbl), ("strike", _dbl), ("r", _dbl), ("sigma", _dbl), ("t", _dbl), ("steps", _i64),
+                ("path_offset", _i64), ("output_kind", _i64)]
+
+
+class GrayScottParams(ctypes.Structure):
+    _fields_ = [("du", _dbl), ("dv", _dbl), ("f", _dbl), ("k", _dbl), ("dt", _dbl), ("steps", _i64),
+                ("rows", _i64), ("cols", _i64), ("halo", _i64)]
+
+
+class LvRk4Df32Params(ctypes.Structure):
+    _fields_ = [("dt", _dbl), ("steps", _i64)]
+
+
+class KeplerRk4Df32Params(ctypes.Structure):
+    _fields_ = [("dt", _dbl), ("gm", _dbl), ("steps", _i64)]
+
+
+class ThreefryParams(ctypes.Structure):
+    _fields_ = [("op", _i64), ("count", _i64)]
+
+
+class LaunchInfo(ctypes.Structure):
+    _fields_ = [("kernel_name", ctypes.c_char * 64), ("cuda_grid", _i64 * 3), ("cuda_block", _i64 * 3),
+                ("items_per_thread", _i64), ("launches", _i64), ("scratch_bytes", _i64),
+                ("regs_per_thread", ctypes.c_int32), ("static_smem_bytes", ctypes.c_int32),
+                ("dynamic_smem_bytes", ctypes.c_int32), ("blocks_per_sm", ctypes.c_int32)]
+
+
+def library_path() -> Path:
+    override = os.environ.get("PALLADIUM_FFI_LIBRARY")
+    if override:
+        return Path(override)
+    return Path(__file__).resolve().parent / _LIBRARY_NAME
+
+
+_LOAD_LOCK = threading.Lock()
+_lib: ctypes.CDLL | None = None
+
+
+def _declare(lib: ctypes.CDLL) -> None:
+    vp, sz, ci = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    i64p = ctypes.POINTER(_i64)
+    vpp = ctypes.POINTER(vp)
+    szp = ctypes.POINTER(sz)
+    cp = ctypes.c_char_p
+    lib.pd_version.restype = ci
+    lib.pd_version.argtypes = []
+    lib.pd_device_count.restype = ci
+    lib.pd_device_count.argtypes = []
+    lib.pd_launch.restype = ci
+    lib.pd_launch.argtypes = [ci, vp, sz, ci, i64p, i64p, ci, vpp, szp, ci, vpp, szp, vp, sz, vp, cp, sz]
+    lib.pd_dispatch_host.restype = ci
+    lib.pd_dispatch_host.argtypes = [ci, vp, sz, ci, i64p, i64p, ci, vpp, szp, ci, vpp, szp, cp, sz]
+    lib.pd_explain.restype = ci
+    lib.pd_explain.argtypes = [ci, vp, sz, ci, i64p, i64p, ctypes.POINTER(LaunchInfo), cp, sz]
+    lib.pd_set_tuning.restype = ci
+    lib.pd_set_tuning.argtypes = [cp, _i64]
+    lib.pd_get_tuning.restype = ci
+    lib.pd_get_tuning.argtypes = [cp, i64p]
+    lib.pd_measure_fp32_fma_peak.restype = ci
+    lib.pd_measure_fp32_fma_peak.argtypes = [ctypes.POINTER(_dbl), cp, sz]
+    lib.pd_measure_int32_alu_peak.restype = ci
+    lib.pd_measure_int32_alu_peak.argtypes = [ctypes.POINTER(_dbl), cp, sz]
+    lib.pd_last_kernel_ms.restype = _dbl
+    lib.pd_last_kernel_ms.argtypes = []
+
+
+def library() -> ctypes.CDLL:
+    """Load the native library once per process (locked: concurrent first
+    calls must not both run the body, as in src/palladium/ffi.py:64-79)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _LOAD_LOCK:
+        if _lib is not None:
+            return _lib
+        path = library_path()
+        if not path.is_file():
+            raise EmitError(
+                f"palladium_b200's CUDA library ({path}) isn't built. Build it with "
+                "`python -m palladium_b200.build` (needs nvcc), or set PALLADIUM_FFI_LIBRARY "
+                "to an existing build. There is no CPU fallback."
+            )
+        lib = ctypes.CDLL(str(path))
+        _declare(lib)
+        version = lib.pd_version()
+        if version != PD_ABI_VERSION:
+            raise EmitError(f"{path} has ABI version {version}, this package expects {PD_ABI_VERSION}; rebuild it")
+        _lib = lib
+    return _lib
+
+
+_ERR_CAP = 1024
+
+
+def _raise(code: int, message: bytes) -> None:
+    text = message.decode("utf-8", "replace") or f"native call failed with status {code}"
+    if code == 1:
+        raise DispatchError(text)
+    if code == 3:
+        raise DispatchError(text) if "no CUDA device" in text else PalladiumError(text)
+    raise PalladiumError(text)
+
+
+def _arrays(grid, block):
+    g = tuple(int(x) for x in grid) + (1, 1, 1)
+    garr = (_i64 * 3)(*g[:3])
+    if block is None:
+        barr = (_i64 * 3)(0, 0, 0)
+    else:
+        b = (int(block),) if isinstance(block, int) else tuple(int(x) for x in block)
+        b = b + (1, 1, 1)
+        barr = (_i64 * 3)(*b[:3])
+    return garr, barr
+
+
+def _buffers(ptrs_and_bytes):
+    n = len(ptrs_and_bytes)
+    ptrs = (ctypes.c_void_p * max(n, 1))(*[p for p, _ in ptrs_and_bytes])
+    sizes = (ctypes.c_size_t * max(n, 1))(*[b for _, b in ptrs_and_bytes])
+    return n, ptrs, sizes
+
+
+def launch(family: int, params: ctypes.Structure, math_mode: int, grid, block, inputs, outputs, stream: int = 0,
+           workspace: tuple[int, int] | None = None) -> None:
+    """pd_launch on device pointers. inputs / outputs: lists of (pointer, bytes)."""
+    lib = library()
+    garr, barr = _arrays(grid, block)
+    n_in, in_ptrs, in_sizes = _buffers(inputs)
+    n_out, out_ptrs, out_sizes = _buffers(outputs)
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    ws_ptr, ws_bytes = workspace if workspace else (None, 0)
+    rc = lib.pd_launch(family, ctypes.addressof(params), ctypes.sizeof(params), math_mode, garr, barr, n_in, in_ptrs,
+                       in_sizes, n_out, out_ptrs, out_sizes, ws_ptr, ws_bytes, stream or None, err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+
+
+def dispatch_host(family: int, params: ctypes.Structure, math_mode: int, grid, block, inputs, outputs) -> None:
+    """pd_dispatch_host on host pointers (blocking)."""
+    lib = library()
+    garr, barr = _arrays(grid, block)
+    n_in, in_ptrs, in_sizes = _buffers(inputs)
+    n_out, out_ptrs, out_sizes = _buffers(outputs)
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = lib.pd_dispatch_host(family, ctypes.addressof(params), ctypes.sizeof(params), math_mode, garr, barr, n_in,
+                              in_ptrs, in_sizes, n_out, out_ptrs, out_sizes, err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+
+
+def explain(family: int, params: ctypes.Structure, math_mode: int, grid, block) -> LaunchInfo:
+    lib = library()
+    garr, barr = _arrays(grid, block)
+    info = LaunchInfo()
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = lib.pd_explain(family, ctypes.addressof(params), ctypes.sizeof(params), math_mode, garr, barr,
+                        ctypes.byref(info), err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    return info
+
+
+def set_tuning(key: str, value: int) -> None:
+    if library().pd_set_tuning(key.encode(), int(value)):
+        raise KeyError(f"unknown tuning key {key!r}")
+
+
+def get_tuning(key: str) -> int:
+    out = _i64(0)
+    if library().pd_get_tuning(key.encode(), ctypes.byref(out)):
+        raise KeyError(f"unknown tuning key {key!r}")
+    return int(out.value)
+
+
+def device_count() -> int:
+    return int(library().pd_device_count())
+
+
+def measure_fp32_fma_peak() -> float:
+    out = _dbl(0.0)
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_measure_fp32_fma_peak(ctypes.byref(out), err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    return float(out.value)
+
+
+def measure_int32_alu_peak() -> float:
+    out = _dbl(0.0)
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_measure_int32_alu_peak(ctypes.byref(out), err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    return float(out.value)
+
+
+def last_kernel_ms() -> float:
+    return float(library().pd_last_kernel_ms())

@@ -1,0 +1,792 @@
+// pd_api.cu -- the C ABI of libpalladium_cuda.so (declared in
+// include/palladium_cuda.h).  This file is the CUDA counterpart of the
+// reference's XLA-FFI handler (native/ffi/palladium_ffi.cpp): it validates a
+// call, picks the launch geometry, owns the little device scratch the kernels
+// need, and launches them.  It never owns caller data.
+#include "../../include/palladium_cuda.h"
+#include "pd_kernels.h"
+
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------
+int fail(int code, char* err, size_t cap, const char* fmt, ...) {
+    if (err && cap) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(err, cap, fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+#define PD_CUDA_TRY(expr)                                                                   \
+    do {                                                                                    \
+        cudaError_t e_ = (expr);                                                            \
+        if (e_ != cudaSuccess)                                                              \
+            return fail(PD_ERR_CUDA, err, err_cap, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
+    } while (0)
+
+// ---------------------------------------------------------------------------
+// tuning knobs
+// ---------------------------------------------------------------------------
+std::mutex g_tuning_mutex;
+std::map<std::string, int64_t>& tuning() {
+    static std::map<std::string, int64_t> t = {
+        {"lv_items_per_thread", 0},  // 0 = choose from N and alignment
+        {"lv_block", 0},             // 0 = choose from N
+        {"vdp_variant", 1},          // 0 direct, 1 persistent warps with lane refill
+        {"vdp_block", 128},
+        {"vdp_blocks_per_sm", 0},    // 0 = from the occupancy calculator
+        {"gbm_block", 256},
+        {"gbm_blocks_per_sm", 0},
+        {"gs_variant", -1},          // -1 = vec4 when the shape allows, else per-cell
+        {"df32_block", 128},
+        {"time_kernels", 0},
+    };
+    return t;
+}
+int64_t knob(const char* key) {
+    std::lock_guard<std::mutex> lock(g_tuning_mutex);
+    return tuning()[key];
+}
+
+// ---------------------------------------------------------------------------
+// device facts
+// ---------------------------------------------------------------------------
+struct DeviceFacts { int device = -1; int sms = 148; bool present = false; };
+DeviceFacts device_facts() {
+    DeviceFacts f;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return f;
+    }
+    if (cudaGetDevice(&f.device) != cudaSuccess) { cudaGetLastError(); return f; }
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, f.device) == cudaSuccess && sms > 0)
+        f.sms = sms;
+    f.present = true;
+    return f;
+}
+
+const PdModeTable* mode_table(int math_mode) {
+    switch (math_mode) {
+        case PD_MATH_SAFE: return pd_mode_table_safe();
+        case PD_MATH_RELAXED: return pd_mode_table_relaxed();
+        case PD_MATH_FAST: return pd_mode_table_fast();
+        default: return nullptr;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// scratch pool: one grow-only device buffer per (device, stream).  Work on one
+// stream is ordered, so consecutive calls can share the buffer.
+// ---------------------------------------------------------------------------
+struct ScratchSlot { void* ptr = nullptr; size_t bytes = 0; };
+std::mutex g_scratch_mutex;
+std::map<std::pair<int, void*>, ScratchSlot>& scratch_pool() {
+    static std::map<std::pair<int, void*>, ScratchSlot> pool;
+    return pool;
+}
+cudaError_t scratch_get(int device, void* stream, size_t bytes, void** out) {
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    ScratchSlot& slot = scratch_pool()[std::make_pair(device, stream)];
+    if (slot.bytes < bytes) {
+        if (slot.ptr) {
+            cudaError_t e = cudaFree(slot.ptr);  // synchronises: no kernel still reads it
+            if (e != cudaSuccess) return e;
+            slot.ptr = nullptr;
+            slot.bytes = 0;
+        }
+        size_t want = bytes < 4096 ? 4096 : bytes;
+        cudaError_t e = cudaMalloc(&slot.ptr, want);
+        if (e != cudaSuccess) return e;
+        slot.bytes = want;
+    }
+    *out = slot.ptr;
+    return cudaSuccess;
+}
+
+thread_local double t_last_kernel_ms = -1.0;
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// ---------------------------------------------------------------------------
+// launch plans: everything pd_explain reports and pd_launch needs
+// ---------------------------------------------------------------------------
+struct Plan {
+    const char* kernel_name = "";
+    int64_t grid[3] = {1, 1, 1};
+    int64_t block[3] = {1, 1, 1};
+    int64_t items = 1;
+    int64_t launches = 1;
+    int64_t scratch_bytes = 0;
+    int variant = 0;
+    const void* kernel = nullptr;
+};
+
+int requested_block(const int64_t block[3]) {
+    if (!block) return 0;
+    int64_t b = block[0] * (block[1] > 0 ? block[1] : 1) * (block[2] > 0 ? block[2] : 1);
+    return b > 0 ? (int)b : 0;
+}
+
+int check_block(int b, char* err, size_t err_cap) {
+    if (b < 32 || b > 256 || (b % 32) != 0)
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                    "threadgroup of %d threads is not supported: use a multiple of 32 in [32, 256]", b);
+    return PD_OK;
+}
+
+int occupancy_blocks(const void* kernel, int block) {
+    int n = 0;
+    if (!kernel || cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, block, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+template <class P>
+int get_params(const void* params, size_t bytes, const P** out, const char* what, char* err, size_t err_cap) {
+    if (!params || bytes != sizeof(P))
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "%s: params block must be %zu bytes, got %zu", what,
+                    sizeof(P), params ? bytes : (size_t)0);
+    *out = static_cast<const P*>(params);
+    return PD_OK;
+}
+
+int lv_items_for(int64_t n, int sms, bool vec_ok) {
+    int64_t forced = knob("lv_items_per_thread");
+    if (forced == 1 || forced == 2 || forced == 4) return vec_ok ? (int)forced : 1;
+    if (!vec_ok) return 1;
+    // Keep at least ~2048 threads per SM before trading threads for per-thread ILP.
+    if (n >= (int64_t)4 * sms * 2048) return 4;
+    if (n >= (int64_t)2 * sms * 2048) return 2;
+    return 1;
+}
+
+int build_plan(int family, const void* params, size_t params_bytes, int math_mode, const int64_t grid[3],
+               const int64_t block[3], bool vec_ok, const DeviceFacts& dev, Plan* plan, char* err,
+               size_t err_cap) {
+    if (math_mode < PD_MATH_SAFE || math_mode > PD_MATH_FAST)
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "palladium_dispatch: math_mode out of range");
+    if (!grid) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "grid must not be NULL");
+    for (int i = 0; i < 3; ++i)
+        if (grid[i] < 0) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "grid[%d] is negative", i);
+    const PdModeTable* mt = mode_table(math_mode);
+    const int req_block = requested_block(block);
+    if (req_block) {
+        int rc = check_block(req_block, err, err_cap);
+        if (rc) return rc;
+    }
+    const int64_t n = grid[0];
+    switch (family) {
+        case PD_FAMILY_LV_RK4: {
+            const pd_lv_rk4_params* p;
+            int rc = get_params(params, params_bytes, &p, "lv_rk4", err, err_cap);
+            if (rc) return rc;
+            if (p->steps < 0 || p->steps > INT32_MAX)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "lv_rk4: steps out of range");
+            const int items = lv_items_for(n, dev.sms, vec_ok);
+            int b = req_block ? req_block : (int)knob("lv_block");
+            if (!b) b = (n / items >= (int64_t)dev.sms * 2048) ? 128 : 64;
+            plan->kernel_name = items == 4 ? "pd_lv_rk4_kernel<4>" : items == 2 ? "pd_lv_rk4_kernel<2>" : "pd_lv_rk4_kernel<1>";
+            plan->items = items;
+            plan->block[0] = b;
+            plan->grid[0] = ((n + items - 1) / items + b - 1) / b;
+            plan->variant = items;
+            plan->kernel = mt->kernel_ptr(family, items);
+            return PD_OK;
+        }
+        case PD_FAMILY_VDP_BS32: {
+            const pd_vdp_bs32_params* p;
+            int rc = get_params(params, params_bytes, &p, "vdp_bs32", err, err_cap);
+            if (rc) return rc;
+            if (p->max_steps < 0 || p->max_steps > (1 << 24))
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                            "vdp_bs32: max_steps must lie in [0, 2^24] (the reference counts in float32)");
+            if (p->out_layout < 0 || p->out_layout > 2)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "vdp_bs32: out_layout must be 0, 1 or 2");
+            if (p->error_order <= 0)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "vdp_bs32: error_order must be positive");
+            const int variant = (int)knob("vdp_variant");
+            int b = req_block ? req_block : (int)knob("vdp_block");
+            plan->variant = variant;
+            plan->kernel = mt->kernel_ptr(family, variant);
+            plan->block[0] = b;
+            if (variant == 0) {
+                plan->kernel_name = "pd_vdp_direct_kernel";
+                plan->grid[0] = (n + b - 1) / b;
+            } else {
+                plan->kernel_name = "pd_vdp_refill_kernel";
+                int per_sm = (int)knob("vdp_blocks_per_sm");
+                if (!per_sm) per_sm = dev.present ? occupancy_blocks(plan->kernel, b) : 0;
+                if (per_sm <= 0) per_sm = 2048 / b / 2;
+                int64_t g = (int64_t)dev.sms * per_sm;
+                const int64_t needed = (n + b - 1) / b;
+                if (g > needed) g = needed;
+                plan->grid[0] = g > 0 ? g : 1;
+                plan->scratch_bytes = 256;
+            }
+            return PD_OK;
+        }
+        case PD_FAMILY_GBM_THREEFRY: {
+            const pd_gbm_params* p;
+            int rc = get_params(params, params_bytes, &p, "gbm_threefry", err, err_cap);
+            if (rc) return rc;
+            if (p->steps < 0 || p->steps > (1 << 30))
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gbm_threefry: steps out of range");
+            if (p->path_offset < 0 || p->path_offset + n > ((int64_t)1 << 32))
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                            "gbm_threefry: path indices must fit in 32 bits (fold_in takes a uint32)");
+            int b = req_block ? req_block : (int)knob("gbm_block");
+            plan->kernel_name = "pd_gbm_kernel";
+            plan->kernel = mt->kernel_ptr(family, 0);
+            int per_sm = (int)knob("gbm_blocks_per_sm");
+            if (!per_sm) per_sm = dev.present ? occupancy_blocks(plan->kernel, b) : 0;
+            if (per_sm <= 0) per_sm = 2048 / b / 2;
+            int64_t g = (int64_t)dev.sms * per_sm;
+            const int64_t needed = (n + b - 1) / b;
+            if (g > needed) g = needed;
+            plan->grid[0] = g > 0 ? g : 1;
+            plan->block[0] = b;
+            plan->launches = 2;
+            plan->scratch_bytes = (int64_t)plan->grid[0] * 2 * sizeof(double);
+            return PD_OK;
+        }
+        case PD_FAMILY_GRAY_SCOTT: {
+            const pd_gray_scott_params* p;
+            int rc = get_params(params, params_bytes, &p, "gray_scott", err, err_cap);
+            if (rc) return rc;
+            if (p->rows <= 0 || p->cols <= 0 || p->rows > (1 << 20) || p->cols > (1 << 20))
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott: rows/cols out of range");
+            if (grid[0] != p->rows || grid[1] != p->cols)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                            "gray_scott: grid (%lld, %lld) does not match rows x cols (%lld, %lld)",
+                            (long long)grid[0], (long long)grid[1], (long long)p->rows, (long long)p->cols);
+            if (p->steps < 0) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott: steps is negative");
+            if (p->halo < 0) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott: halo is negative");
+            if (p->halo > 0 && p->steps > p->halo)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                            "gray_scott: a slab with %lld halo rows can advance at most %lld steps per call",
+                            (long long)p->halo, (long long)p->halo);
+            const int64_t rows_alloc = p->rows + 2 * p->halo;
+            if (rows_alloc * p->cols >= ((int64_t)1 << 31))
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott: more than 2^31 cells per call");
+            int variant = (int)knob("gs_variant");
+            const bool vec_shape = (p->cols % 4 == 0) && p->cols >= 128 && vec_ok;
+            if (variant < 0) variant = vec_shape ? 1 : 0;
+            if (variant == 1 && !vec_shape) variant = 0;
+            plan->variant = variant;
+            plan->kernel = mt->kernel_ptr(family, variant);
+            if (variant == 0) {
+                plan->kernel_name = "pd_gs_cell_kernel";
+                plan->block[0] = 32; plan->block[1] = 8;
+                plan->grid[0] = (p->cols + 31) / 32;
+                plan->grid[1] = (rows_alloc + 7) / 8;
+            } else {
+                plan->kernel_name = "pd_gs_vec4_kernel";
+                plan->items = 4 * PD_GS_TILE_ROWS;
+                plan->block[0] = PD_GS_BLOCK;
+                plan->grid[0] = (p->cols / 4 + PD_GS_BLOCK - 1) / PD_GS_BLOCK;
+                plan->grid[1] = (rows_alloc + PD_GS_TILE_ROWS - 1) / PD_GS_TILE_ROWS;
+            }
+            plan->launches = p->steps;
+            plan->scratch_bytes = p->steps >= 2 ? 2 * rows_alloc * p->cols * (int64_t)sizeof(float) : 0;
+            return PD_OK;
+        }
+        case PD_FAMILY_LV_RK4_DF32:
+        case PD_FAMILY_KEPLER_RK4_DF32: {
+            int64_t steps;
+            if (family == PD_FAMILY_LV_RK4_DF32) {
+                const pd_lv_rk4_df32_params* p;
+                int rc = get_params(params, params_bytes, &p, "lv_rk4_df32", err, err_cap);
+                if (rc) return rc;
+                steps = p->steps;
+                plan->kernel_name = "pd_lv_df32_kernel";
+            } else {
+                const pd_kepler_rk4_df32_params* p;
+                int rc = get_params(params, params_bytes, &p, "kepler_rk4_df32", err, err_cap);
+                if (rc) return rc;
+                steps = p->steps;
+                plan->kernel_name = "pd_kepler_df32_kernel";
+            }
+            if (steps < 0 || steps > INT32_MAX)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "df32: steps out of range");
+            int b = req_block ? req_block : (int)knob("df32_block");
+            plan->block[0] = b;
+            plan->grid[0] = (n + b - 1) / b;
+            plan->kernel = pd_common_kernel_ptr(family);
+            return PD_OK;
+        }
+        case PD_FAMILY_THREEFRY_BITS: {
+            const pd_threefry_params* p;
+            int rc = get_params(params, params_bytes, &p, "threefry_bits", err, err_cap);
+            if (rc) return rc;
+            if (p->op < 0 || p->op > 3)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "threefry_bits: op must be 0..3");
+            if (p->op == 3 && p->count <= 0)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "threefry_bits: count must be positive");
+            const int64_t total = p->op == 3 ? n * p->count : n;
+            if (total >= ((int64_t)1 << 32))
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "threefry_bits: more than 2^32 draws");
+            int b = req_block ? req_block : 256;
+            plan->kernel_name = "pd_threefry_kernel";
+            plan->block[0] = b;
+            plan->grid[0] = (total + b - 1) / b;
+            plan->kernel = pd_common_kernel_ptr(family);
+            return PD_OK;
+        }
+        default:
+            return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "unknown kernel family %d", family);
+    }
+}
+
+int check_buffers(const char* what, int n_have, int n_want, const size_t* bytes, const size_t* want_bytes,
+                  const void* const* ptrs, char* err, size_t err_cap) {
+    if (n_have != n_want)
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "kernel takes %d %s arrays, got %d", n_want, what, n_have);
+    for (int i = 0; i < n_want; ++i) {
+        if (bytes[i] != want_bytes[i])
+            return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "%s %d: expected %zu bytes, got %zu", what, i,
+                        want_bytes[i], bytes[i]);
+        if (want_bytes[i] && !ptrs[i])
+            return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "%s %d: NULL pointer", what, i);
+        if (!aligned(ptrs[i], 4))
+            return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "%s %d: pointer is not 4-byte aligned", what, i);
+    }
+    return PD_OK;
+}
+
+bool all_aligned16(int n_in, const void* const* in, int n_out, void* const* out) {
+    for (int i = 0; i < n_in; ++i) if (!aligned(in[i], 16)) return false;
+    for (int i = 0; i < n_out; ++i) if (!aligned(out[i], 16)) return false;
+    return true;
+}
+
+// Expected buffer sizes for a family call.
+int expected_sizes(int family, const void* params, const int64_t grid[3], std::vector<size_t>* in,
+                   std::vector<size_t>* out, int n_out_given, char* err, size_t err_cap) {
+    const size_t n = (size_t)grid[0];
+    switch (family) {
+        case PD_FAMILY_LV_RK4:
+        case PD_FAMILY_LV_RK4_DF32:
+            in->assign(6, 4 * n); out->assign(2, 4 * n); return PD_OK;
+        case PD_FAMILY_VDP_BS32: {
+            const pd_vdp_bs32_params* p = static_cast<const pd_vdp_bs32_params*>(params);
+            in->assign(3, 4 * n);
+            if (p->out_layout == 0) out->assign(6, 4 * n);
+            else if (p->out_layout == 1) out->assign(5, 4 * n);
+            else { out->assign(3, 4 * n); (*out)[0] = 8 * n; }
+            return PD_OK;
+        }
+        case PD_FAMILY_GBM_THREEFRY:
+            in->assign(1, 8);
+            out->assign(1, 4 * n);
+            if (n_out_given == 2) out->push_back(16);
+            return PD_OK;
+        case PD_FAMILY_GRAY_SCOTT: {
+            const pd_gray_scott_params* p = static_cast<const pd_gray_scott_params*>(params);
+            const size_t cells = (size_t)(p->rows + 2 * p->halo) * (size_t)p->cols;
+            in->assign(2, 4 * cells); out->assign(2, 4 * cells); return PD_OK;
+        }
+        case PD_FAMILY_KEPLER_RK4_DF32:
+            in->assign(8, 4 * n); out->assign(8, 4 * n); return PD_OK;
+        case PD_FAMILY_THREEFRY_BITS: {
+            const pd_threefry_params* p = static_cast<const pd_threefry_params*>(params);
+            in->assign(1, 8);
+            if (p->op == 2) { in->push_back(4 * n); out->assign(1, 8 * n); }
+            else if (p->op == 3) out->assign(1, 4 * n * (size_t)p->count);
+            else out->assign(1, 4 * n);
+            return PD_OK;
+        }
+        default:
+            return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "unknown kernel family %d", family);
+    }
+}
+
+void split_df32(double v, float* hi, float* lo) {
+    *hi = (float)v;
+    *lo = (float)(v - (double)*hi);
+}
+
+int launch_impl(int family, const void* params, size_t params_bytes, int math_mode, const int64_t grid[3],
+                const int64_t block[3], int n_in, const void* const* in, const size_t* in_bytes, int n_out,
+                void* const* out, const size_t* out_bytes, void* workspace, size_t workspace_bytes,
+                cudaStream_t st, char* err, size_t err_cap) {
+    DeviceFacts dev = device_facts();
+    if (!dev.present)
+        return fail(PD_ERR_CUDA, err, err_cap,
+                    "no CUDA device is available: libpalladium_cuda has no CPU fallback");
+    if ((n_in > 0 && (!in || !in_bytes)) || (n_out > 0 && (!out || !out_bytes)))
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "buffer arrays must not be NULL");
+    const bool vec_ok = all_aligned16(n_in, in, n_out, out);
+    Plan plan;
+    int rc = build_plan(family, params, params_bytes, math_mode, grid, block, vec_ok, dev, &plan, err, err_cap);
+    if (rc) return rc;
+    std::vector<size_t> want_in, want_out;
+    rc = expected_sizes(family, params, grid, &want_in, &want_out, n_out, err, err_cap);
+    if (rc) return rc;
+    rc = check_buffers("input", n_in, (int)want_in.size(), in_bytes, want_in.data(), in, err, err_cap);
+    if (rc) return rc;
+    rc = check_buffers("output", n_out, (int)want_out.size(), out_bytes, want_out.data(),
+                       const_cast<const void* const*>(out), err, err_cap);
+    if (rc) return rc;
+
+    void* scratch = nullptr;
+    if (plan.scratch_bytes > 0) {
+        if (workspace) {
+            if (workspace_bytes < (size_t)plan.scratch_bytes)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "workspace of %zu bytes is smaller than the %lld needed",
+                            workspace_bytes, (long long)plan.scratch_bytes);
+            if (!aligned(workspace, 256))
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "workspace must be 256-byte aligned");
+            scratch = workspace;
+        } else {
+            PD_CUDA_TRY(scratch_get(dev.device, (void*)st, (size_t)plan.scratch_bytes, &scratch));
+        }
+    }
+
+    const bool timed = knob("time_kernels") != 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    t_last_kernel_ms = -1.0;
+    if (timed) {
+        PD_CUDA_TRY(cudaEventCreate(&ev0));
+        PD_CUDA_TRY(cudaEventCreate(&ev1));
+        PD_CUDA_TRY(cudaEventRecord(ev0, st));
+    }
+
+    const PdModeTable* mt = mode_table(math_mode);
+    const int64_t n = grid[0];
+    const int b = (int)plan.block[0];
+    switch (family) {
+        case PD_FAMILY_LV_RK4: {
+            const pd_lv_rk4_params* p = static_cast<const pd_lv_rk4_params*>(params);
+            PdLvArgs a;
+            a.x0 = (const float*)in[0]; a.y0 = (const float*)in[1]; a.a = (const float*)in[2];
+            a.b = (const float*)in[3]; a.c = (const float*)in[4]; a.d = (const float*)in[5];
+            a.xo = (float*)out[0]; a.yo = (float*)out[1];
+            a.n = n; a.steps = (int)p->steps;
+            a.h_half = (float)(0.5 * p->dt); a.h_full = (float)p->dt;
+            a.h_sixth = (float)(p->dt / 6.0); a.h_third = (float)(p->dt / 3.0);
+            PD_CUDA_TRY(mt->lv_rk4(a, (int)plan.items, b, st));
+            break;
+        }
+        case PD_FAMILY_VDP_BS32: {
+            const pd_vdp_bs32_params* p = static_cast<const pd_vdp_bs32_params*>(params);
+            PdVdpArgs a;
+            memset(&a, 0, sizeof(a));
+            a.x0 = (const float*)in[0]; a.v0 = (const float*)in[1]; a.mu = (const float*)in[2];
+            if (p->out_layout == 2) {
+                if (!aligned(out[0], 8))
+                    return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output 0: (N,2) state must be 8-byte aligned");
+                a.state2_out = (float*)out[0];
+                a.accepted_i32 = (int32_t*)out[1];
+                a.rejected_i32 = (int32_t*)out[2];
+            } else {
+                a.t_out = (float*)out[0]; a.x_out = (float*)out[1]; a.v_out = (float*)out[2];
+                a.steps_out = (float*)out[3]; a.rejected_out = (float*)out[4];
+                if (p->out_layout == 0) a.real_out = (float*)out[5];
+            }
+            a.n = n; a.max_steps = (int)p->max_steps;
+            a.t1 = (float)p->t1; a.rtol = (float)p->rtol; a.atol = (float)p->atol; a.dt0 = (float)p->dt0;
+            a.safety = (float)p->safety; a.factor_min = (float)p->factor_min; a.factor_max = (float)p->factor_max;
+            a.coeff1 = (float)((p->icoeff + p->pcoeff) / (double)p->error_order);
+            a.coeff2 = (float)(-p->pcoeff / (double)p->error_order);
+            if (plan.variant == 1) {
+                a.cursor = (unsigned long long*)scratch;
+                PD_CUDA_TRY(cudaMemsetAsync(scratch, 0, 256, st));
+            }
+            PD_CUDA_TRY(mt->vdp_bs32(a, plan.variant, (int)plan.grid[0], b, st));
+            break;
+        }
+        case PD_FAMILY_GBM_THREEFRY: {
+            const pd_gbm_params* p = static_cast<const pd_gbm_params*>(params);
+            PdGbmArgs a;
+            a.key = (const uint32_t*)in[0];
+            a.out = (float*)out[0];
+            a.block_partials = (n_out == 2) ? (double*)scratch : nullptr;
+            a.n = n; a.path_offset = (uint32_t)p->path_offset; a.steps = (int)p->steps;
+            a.output_kind = (int)p->output_kind;
+            const double dt = p->t / (double)(p->steps > 0 ? p->steps : 1);
+            a.s0 = (float)p->s0; a.strike = (float)p->strike;
+            a.drift_dt = (float)((p->r - p->sigma * p->sigma / 2.0) * dt);
+            a.vol_sqdt = (float)p->sigma * sqrtf((float)dt);
+            if (n_out == 2 && !aligned(out[1], 8))
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output 1: float64 sums must be 8-byte aligned");
+            PD_CUDA_TRY(mt->gbm(a, (int)plan.grid[0], b, st));
+            if (n_out == 2) {
+                if (n > 0) PD_CUDA_TRY(pd_launch_gbm_finish((const double*)scratch, (int)plan.grid[0], (double*)out[1], st));
+                else PD_CUDA_TRY(cudaMemsetAsync(out[1], 0, 16, st));
+            }
+            break;
+        }
+        case PD_FAMILY_GRAY_SCOTT: {
+            const pd_gray_scott_params* p = static_cast<const pd_gray_scott_params*>(params);
+            const int rows_alloc = (int)(p->rows + 2 * p->halo);
+            const size_t field_bytes = (size_t)rows_alloc * (size_t)p->cols * sizeof(float);
+            PdGsArgs a;
+            a.rows_alloc = rows_alloc; a.cols = (int)p->cols;
+            a.periodic_rows = p->halo == 0 ? 1 : 0;
+            a.du = (float)p->du; a.dv = (float)p->dv; a.f = (float)p->f; a.fk = (float)(p->f + p->k);
+            a.dt = (float)p->dt;
+            if (p->steps == 0) {
+                PD_CUDA_TRY(cudaMemcpyAsync(out[0], in[0], field_bytes, cudaMemcpyDeviceToDevice, st));
+                PD_CUDA_TRY(cudaMemcpyAsync(out[1], in[1], field_bytes, cudaMemcpyDeviceToDevice, st));
+                break;
+            }
+            float* ping_u = (float*)out[0];
+            float* ping_v = (float*)out[1];
+            float* pong_u = (float*)scratch;
+            float* pong_v = scratch ? (float*)((char*)scratch + field_bytes) : nullptr;
+            const float* src_u = (const float*)in[0];
+            const float* src_v = (const float*)in[1];
+            // The last step must land in `out`: odd step counts start there.
+            bool to_out = (p->steps % 2) == 1;
+            for (int64_t s = 1; s <= p->steps; ++s) {
+                a.u = src_u; a.v = src_v;
+                a.uo = to_out ? ping_u : pong_u;
+                a.vo = to_out ? ping_v : pong_v;
+                if (p->halo == 0) { a.row_lo = 0; a.row_hi = rows_alloc; }
+                else { a.row_lo = (int)s; a.row_hi = rows_alloc - (int)s; }
+                PD_CUDA_TRY(mt->gray_scott(a, plan.variant, st));
+                src_u = a.uo; src_v = a.vo;
+                to_out = !to_out;
+            }
+            break;
+        }
+        case PD_FAMILY_LV_RK4_DF32: {
+            const pd_lv_rk4_df32_params* p = static_cast<const pd_lv_rk4_df32_params*>(params);
+            PdDfLvArgs a;
+            a.x0 = (const float*)in[0]; a.y0 = (const float*)in[1]; a.a = (const float*)in[2];
+            a.b = (const float*)in[3]; a.c = (const float*)in[4]; a.d = (const float*)in[5];
+            a.xo = (float*)out[0]; a.yo = (float*)out[1];
+            a.n = n; a.steps = (int)p->steps; a.dt = (float)p->dt;
+            PD_CUDA_TRY(pd_launch_lv_df32(a, b, st));
+            break;
+        }
+        case PD_FAMILY_KEPLER_RK4_DF32: {
+            const pd_kepler_rk4_df32_params* p = static_cast<const pd_kepler_rk4_df32_params*>(params);
+            PdKeplerArgs a;
+            for (int i = 0; i < 8; ++i) { a.in[i] = (const float*)in[i]; a.out[i] = (float*)out[i]; }
+            a.n = n; a.steps = (int)p->steps;
+            split_df32(p->dt, &a.dt_hi, &a.dt_lo);
+            split_df32(p->gm, &a.gm_hi, &a.gm_lo);
+            PD_CUDA_TRY(pd_launch_kepler_df32(a, b, st));
+            break;
+        }
+        case PD_FAMILY_THREEFRY_BITS: {
+            const pd_threefry_params* p = static_cast<const pd_threefry_params*>(params);
+            PdThreefryArgs a;
+            a.key = (const uint32_t*)in[0];
+            a.data = p->op == 2 ? (const uint32_t*)in[1] : nullptr;
+            a.out = out[0]; a.n = n; a.count = p->count; a.op = (int)p->op;
+            PD_CUDA_TRY(pd_launch_threefry(a, b, st));
+            break;
+        }
+        default:
+            return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "unknown kernel family %d", family);
+    }
+
+    if (timed) {
+        PD_CUDA_TRY(cudaEventRecord(ev1, st));
+        PD_CUDA_TRY(cudaEventSynchronize(ev1));
+        float ms = 0.0f;
+        PD_CUDA_TRY(cudaEventElapsedTime(&ms, ev0, ev1));
+        t_last_kernel_ms = ms;
+        cudaEventDestroy(ev0);
+        cudaEventDestroy(ev1);
+    }
+    return PD_OK;
+}
+
+// Per-thread staging state for pd_dispatch_host.
+struct HostStaging {
+    int device = -1;
+    cudaStream_t stream = nullptr;
+    std::vector<ScratchSlot> slots;
+    ~HostStaging() {
+        // Device memory is reclaimed when the context goes away; freeing here
+        // could run after the runtime has shut down.
+    }
+};
+thread_local HostStaging t_staging;
+
+}  // namespace
+
+extern "C" {
+
+int pd_version(void) { return PD_ABI_VERSION; }
+
+int pd_device_count(void) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return count;
+}
+
+int pd_launch(int family, const void* params, size_t params_bytes, int math_mode, const int64_t grid[3],
+              const int64_t block[3], int n_in, const void* const* in, const size_t* in_bytes, int n_out,
+              void* const* out, const size_t* out_bytes, void* workspace, size_t workspace_bytes,
+              void* cuda_stream, char* err, size_t err_cap) {
+    return launch_impl(family, params, params_bytes, math_mode, grid, block, n_in, in, in_bytes, n_out, out,
+                       out_bytes, workspace, workspace_bytes, (cudaStream_t)cuda_stream, err, err_cap);
+}
+
+int pd_dispatch_host(int family, const void* params, size_t params_bytes, int math_mode, const int64_t grid[3],
+                     const int64_t block[3], int n_in, const void* const* in, const size_t* in_bytes, int n_out,
+                     void* const* out, const size_t* out_bytes, char* err, size_t err_cap) {
+    DeviceFacts dev = device_facts();
+    if (!dev.present)
+        return fail(PD_ERR_CUDA, err, err_cap,
+                    "no CUDA device is available: libpalladium_cuda has no CPU fallback");
+    if (n_in < 0 || n_out < 0 || n_in > 64 || n_out > 64)
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "buffer count out of range");
+    if ((n_in > 0 && (!in || !in_bytes)) || (n_out > 0 && (!out || !out_bytes)))
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "buffer arrays must not be NULL");
+    HostStaging& hs = t_staging;
+    if (hs.device != dev.device) {
+        hs.device = dev.device;
+        hs.stream = nullptr;
+        hs.slots.clear();
+    }
+    if (!hs.stream) PD_CUDA_TRY(cudaStreamCreateWithFlags(&hs.stream, cudaStreamNonBlocking));
+    const int total = n_in + n_out;
+    if ((int)hs.slots.size() < total) hs.slots.resize(total);
+    std::vector<const void*> d_in(n_in);
+    std::vector<void*> d_out(n_out);
+    for (int i = 0; i < total; ++i) {
+        const size_t bytes = i < n_in ? in_bytes[i] : out_bytes[i - n_in];
+        ScratchSlot& slot = hs.slots[i];
+        if (slot.bytes < bytes || !slot.ptr) {
+            if (slot.ptr) PD_CUDA_TRY(cudaFree(slot.ptr));
+            slot.ptr = nullptr; slot.bytes = 0;
+            const size_t want = bytes < 256 ? 256 : bytes;
+            PD_CUDA_TRY(cudaMalloc(&slot.ptr, want));
+            slot.bytes = want;
+        }
+        if (i < n_in) d_in[i] = slot.ptr; else d_out[i - n_in] = slot.ptr;
+    }
+    for (int i = 0; i < n_in; ++i) {
+        if (in_bytes[i] && !in[i]) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "input %d: NULL pointer", i);
+        if (in_bytes[i]) PD_CUDA_TRY(cudaMemcpyAsync(hs.slots[i].ptr, in[i], in_bytes[i], cudaMemcpyHostToDevice, hs.stream));
+    }
+    int rc = launch_impl(family, params, params_bytes, math_mode, grid, block, n_in, d_in.data(), in_bytes, n_out,
+                         d_out.data(), out_bytes, nullptr, 0, hs.stream, err, err_cap);
+    if (rc) {
+        cudaStreamSynchronize(hs.stream);
+        return rc;
+    }
+    for (int i = 0; i < n_out; ++i) {
+        if (out_bytes[i] && !out[i]) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output %d: NULL pointer", i);
+        if (out_bytes[i]) PD_CUDA_TRY(cudaMemcpyAsync(out[i], d_out[i], out_bytes[i], cudaMemcpyDeviceToHost, hs.stream));
+    }
+    PD_CUDA_TRY(cudaStreamSynchronize(hs.stream));
+    return PD_OK;
+}
+
+int pd_explain(int family, const void* params, size_t params_bytes, int math_mode, const int64_t grid[3],
+               const int64_t block[3], pd_launch_info* info, char* err, size_t err_cap) {
+    if (!info) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "info must not be NULL");
+    DeviceFacts dev = device_facts();
+    Plan plan;
+    int rc = build_plan(family, params, params_bytes, math_mode, grid, block, true, dev, &plan, err, err_cap);
+    if (rc) return rc;
+    memset(info, 0, sizeof(*info));
+    snprintf(info->kernel_name, sizeof(info->kernel_name), "%s", plan.kernel_name);
+    for (int i = 0; i < 3; ++i) { info->cuda_grid[i] = plan.grid[i]; info->cuda_block[i] = plan.block[i]; }
+    info->items_per_thread = plan.items;
+    info->launches = plan.launches;
+    info->scratch_bytes = plan.scratch_bytes;
+    info->regs_per_thread = -1;
+    info->static_smem_bytes = -1;
+    info->dynamic_smem_bytes = 0;
+    info->blocks_per_sm = -1;
+    if (dev.present && plan.kernel) {
+        cudaFuncAttributes attr;
+        if (cudaFuncGetAttributes(&attr, plan.kernel) == cudaSuccess) {
+            info->regs_per_thread = attr.numRegs;
+            info->static_smem_bytes = (int32_t)attr.sharedSizeBytes;
+            const int threads = (int)(plan.block[0] * plan.block[1] * plan.block[2]);
+            info->blocks_per_sm = occupancy_blocks(plan.kernel, threads);
+        } else {
+            cudaGetLastError();
+        }
+    }
+    return PD_OK;
+}
+
+int pd_set_tuning(const char* key, int64_t value) {
+    if (!key) return PD_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(g_tuning_mutex);
+    auto it = tuning().find(key);
+    if (it == tuning().end()) return PD_ERR_INVALID_ARGUMENT;
+    it->second = value;
+    return PD_OK;
+}
+
+int pd_get_tuning(const char* key, int64_t* value) {
+    if (!key || !value) return PD_ERR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(g_tuning_mutex);
+    auto it = tuning().find(key);
+    if (it == tuning().end()) return PD_ERR_INVALID_ARGUMENT;
+    *value = it->second;
+    return PD_OK;
+}
+
+static int measure_chain(bool fp, double* out_rate, char* err, size_t err_cap) {
+    if (!out_rate) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "result pointer must not be NULL");
+    DeviceFacts dev = device_facts();
+    if (!dev.present) return fail(PD_ERR_CUDA, err, err_cap, "no CUDA device is available");
+    void* sink = nullptr;
+    PD_CUDA_TRY(cudaMalloc(&sink, 256));
+    cudaEvent_t e0, e1;
+    PD_CUDA_TRY(cudaEventCreate(&e0));
+    PD_CUDA_TRY(cudaEventCreate(&e1));
+    const int grid = dev.sms * 8, block = 256, iters = 4096;
+    double best = 0.0;
+    for (int rep = 0; rep < 5; ++rep) {
+        PD_CUDA_TRY(cudaEventRecord(e0, 0));
+        if (fp) PD_CUDA_TRY(pd_launch_fma_chain((float*)sink, iters, grid, block, 0));
+        else PD_CUDA_TRY(pd_launch_int_chain((uint32_t*)sink, iters, grid, block, 0));
+        PD_CUDA_TRY(cudaEventRecord(e1, 0));
+        PD_CUDA_TRY(cudaEventSynchronize(e1));
+        float ms = 0.0f;
+        PD_CUDA_TRY(cudaEventElapsedTime(&ms, e0, e1));
+        // fp: 8 reps x 8 chains x 2 flops; int: 8 reps x 4 chains x 3 ops
+        const double per_thread = fp ? (double)iters * 8 * 8 * 2 : (double)iters * 8 * 4 * 3;
+        const double rate = per_thread * (double)grid * block / (ms * 1e-3);
+        if (rep > 0 && rate > best) best = rate;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(sink);
+    *out_rate = best;
+    return PD_OK;
+}
+
+int pd_measure_fp32_fma_peak(double* flops_per_s, char* err, size_t err_cap) {
+    return measure_chain(true, flops_per_s, err, err_cap);
+}
+int pd_measure_int32_alu_peak(double* ops_per_s, char* err, size_t err_cap) {
+    return measure_chain(false, ops_per_s, err, err_cap);
+}
+
+double pd_last_kernel_ms(void) { return t_last_kernel_ms; }
+
+}  // extern "C"

@@ -1,0 +1,106 @@
+// pd_kernels.h -- argument blocks and per-math-mode launcher tables shared by
+// the C-ABI layer (pd_api.cu) and the kernel translation unit (pd_kernels.cu),
+// which is compiled once per math mode with a different nvcc flag set:
+//   SAFE    -DPD_MODE=0  -fmad=false -prec-div=true  -prec-sqrt=true  -ftz=false
+//   RELAXED -DPD_MODE=1  -fmad=true  -prec-div=true  -prec-sqrt=true  -ftz=false
+//   FAST    -DPD_MODE=2  -use_fast_math
+#ifndef PD_KERNELS_H_
+#define PD_KERNELS_H_
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+struct PdLvArgs {
+    const float *x0, *y0, *a, *b, *c, *d;
+    float *xo, *yo;
+    int64_t n;
+    int steps;
+    float h_half, h_full, h_sixth, h_third;
+};
+
+struct PdVdpArgs {
+    const float *x0, *v0, *mu;
+    // any output pointer may be null
+    float *t_out, *x_out, *v_out, *steps_out, *rejected_out, *real_out;
+    float *state2_out;
+    int32_t *accepted_i32, *rejected_i32;
+    unsigned long long* cursor;  // work-queue head (scratch, zeroed by the caller)
+    int64_t n;
+    int max_steps;
+    float t1, rtol, atol, dt0, safety, factor_min, factor_max, coeff1, coeff2;
+};
+
+struct PdGbmArgs {
+    const uint32_t* key;
+    float* out;
+    double* block_partials;  // scratch: 2 doubles per block
+    int64_t n;
+    uint32_t path_offset;
+    int steps;
+    int output_kind;
+    float s0, strike, drift_dt, vol_sqdt;
+};
+
+struct PdGsArgs {
+    const float *u, *v;
+    float *uo, *vo;
+    int rows_alloc, cols;
+    int row_lo, row_hi;  // rows updated by this launch: [row_lo, row_hi)
+    int periodic_rows;
+    float du, dv, f, fk, dt;
+};
+
+struct PdDfLvArgs {
+    const float *x0, *y0, *a, *b, *c, *d;
+    float *xo, *yo;
+    int64_t n;
+    int steps;
+    float dt;
+};
+
+struct PdKeplerArgs {
+    const float* in[8];
+    float* out[8];
+    int64_t n;
+    int steps;
+    float dt_hi, dt_lo, gm_hi, gm_lo;
+};
+
+struct PdThreefryArgs {
+    const uint32_t* key;
+    const uint32_t* data;
+    void* out;
+    int64_t n;      // outputs (op 0/1), data items (op 2), groups (op 3)
+    int64_t count;  // draws per group (op 3)
+    int op;
+};
+
+// One table per math mode.
+struct PdModeTable {
+    cudaError_t (*lv_rk4)(const PdLvArgs&, int items_per_thread, int block, cudaStream_t);
+    cudaError_t (*vdp_bs32)(const PdVdpArgs&, int variant, int grid, int block, cudaStream_t);
+    cudaError_t (*gbm)(const PdGbmArgs&, int grid, int block, cudaStream_t);
+    cudaError_t (*gray_scott)(const PdGsArgs&, int variant, cudaStream_t);
+    // kernel entry used for cudaFuncGetAttributes / occupancy in pd_explain
+    const void* (*kernel_ptr)(int family, int variant);
+};
+
+const PdModeTable* pd_mode_table_safe();
+const PdModeTable* pd_mode_table_relaxed();
+const PdModeTable* pd_mode_table_fast();
+
+// Mode-independent kernels (rounding-explicit arithmetic only); they live in
+// the SAFE object.
+cudaError_t pd_launch_lv_df32(const PdDfLvArgs&, int block, cudaStream_t);
+cudaError_t pd_launch_kepler_df32(const PdKeplerArgs&, int block, cudaStream_t);
+cudaError_t pd_launch_threefry(const PdThreefryArgs&, int block, cudaStream_t);
+cudaError_t pd_launch_gbm_finish(const double* partials, int n_blocks, double* sums, cudaStream_t);
+const void* pd_common_kernel_ptr(int family);
+cudaError_t pd_launch_fma_chain(float* sink, int iters, int grid, int block, cudaStream_t);
+cudaError_t pd_launch_int_chain(uint32_t* sink, int iters, int grid, int block, cudaStream_t);
+
+// Gray-Scott geometry, shared by launcher and explain.
+static const int PD_GS_TILE_ROWS = 32;
+static const int PD_GS_BLOCK = 128;
+
+#endif  // PD_KERNELS_H_

@@ -1,0 +1,300 @@
+// pd_math.h -- arithmetic building blocks shared by every kernel family.
+//
+// Everything here compiles both as CUDA device code (nvcc, sm_100a) and as
+// plain C++ on the host, and produces the same bits on both, because each
+// operation is spelled with an explicit rounding (`__fadd_rn`, `__fmul_rn`,
+// `__fmaf_rn`, `__fdiv_rn`, `__fsqrt_rn` on the device; the IEEE operators
+// and `fmaf` on the host, where the translation unit must be built with
+// `-ffp-contract=off`).  No compiler flag (`-fmad`, `-use_fast_math`) can
+// contract, reassociate or approximate what is written through these helpers.
+//
+// Contents
+//   * Threefry-2x32-20 counter RNG, `random_bits`, `fold_in` and the
+//     bits -> uniform[0,1) transform, as specified by the reference emitter
+//     (src/palladium/emit/rules.py:121-201; op chain of `uniform` named at
+//     tests/test_10_random_bits.py:3-7).
+//   * df32 ("double-float") compensated arithmetic: error-free transforms and
+//     add / sub / mul / div / sqrt on (hi, lo) float pairs.  The reference
+//     calls an external prelude for add/sub/mul (examples/05_df32_precision.py:
+//     28-30); these are the textbook algorithms (Knuth TwoSum, Dekker
+//     FastTwoSum, FMA TwoProd).
+//   * pd_powf: a deterministic single-precision pow built only from the
+//     helpers above plus integer bit operations, used by the SAFE build of the
+//     adaptive integrator so that accept/reject decisions are reproducible
+//     bit for bit on any IEEE machine.
+#ifndef PD_MATH_H_
+#define PD_MATH_H_
+
+#include <stdint.h>
+#include <math.h>
+#include <string.h>
+
+#if defined(__CUDACC__)
+#define PD_HD __host__ __device__ __forceinline__
+#else
+#define PD_HD static inline
+#endif
+
+// ---------------------------------------------------------------------------
+// Rounding-explicit scalar operations.
+// ---------------------------------------------------------------------------
+#if defined(__CUDA_ARCH__)
+PD_HD float pd_add(float a, float b) { return __fadd_rn(a, b); }
+PD_HD float pd_sub(float a, float b) { return __fsub_rn(a, b); }
+PD_HD float pd_mul(float a, float b) { return __fmul_rn(a, b); }
+PD_HD float pd_fma(float a, float b, float c) { return __fmaf_rn(a, b, c); }
+PD_HD float pd_div(float a, float b) { return __fdiv_rn(a, b); }
+PD_HD float pd_sqrt(float a) { return __fsqrt_rn(a); }
+PD_HD uint32_t pd_f2u(float f) { return __float_as_uint(f); }
+PD_HD float pd_u2f(uint32_t u) { return __uint_as_float(u); }
+#else
+PD_HD float pd_add(float a, float b) { return a + b; }
+PD_HD float pd_sub(float a, float b) { return a - b; }
+PD_HD float pd_mul(float a, float b) { return a * b; }
+PD_HD float pd_fma(float a, float b, float c) { return fmaf(a, b, c); }
+PD_HD float pd_div(float a, float b) { return a / b; }
+PD_HD float pd_sqrt(float a) { return sqrtf(a); }
+PD_HD uint32_t pd_f2u(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+PD_HD float pd_u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+#endif
+
+// NaN-propagating min / max: the semantics of the staged `max` / `min`
+// primitives the reference kernels use (jnp.maximum / jnp.minimum).
+PD_HD float pd_max_nan(float a, float b) {
+    if (a != a) return a;
+    if (b != b) return b;
+    return a > b ? a : b;
+}
+PD_HD float pd_min_nan(float a, float b) {
+    if (a != a) return a;
+    if (b != b) return b;
+    return a < b ? a : b;
+}
+
+// ---------------------------------------------------------------------------
+// Threefry-2x32-20.
+// ---------------------------------------------------------------------------
+PD_HD uint32_t pd_rotl32(uint32_t v, int r) {
+#if defined(__CUDA_ARCH__)
+    return __funnelshift_l(v, v, r);
+#else
+    return (v << r) | (v >> (32 - r));
+#endif
+}
+
+typedef struct pd_u32x2 { uint32_t a, b; } pd_u32x2;
+
+// One Threefry-2x32-20 block: key (k0, k1), counter words (c0, c1).
+// Five groups of four mix rounds; rotation sets alternate between
+// {13,15,26,6} and {17,29,16,24}; after group g (1-based) the key schedule
+// adds ks[g % 3] to the first word and ks[(g+1) % 3] + g to the second.
+PD_HD pd_u32x2 pd_threefry2x32(uint32_t k0, uint32_t k1, uint32_t c0, uint32_t c1) {
+    const uint32_t ks0 = k0, ks1 = k1, ks2 = k0 ^ k1 ^ 0x1BD11BDAu;
+    uint32_t x0 = c0 + ks0;
+    uint32_t x1 = c1 + ks1;
+#define PD_TF_MIX(R) { x0 += x1; x1 = pd_rotl32(x1, (R)); x1 ^= x0; }
+    PD_TF_MIX(13) PD_TF_MIX(15) PD_TF_MIX(26) PD_TF_MIX(6)
+    x0 += ks1; x1 += ks2 + 1u;
+    PD_TF_MIX(17) PD_TF_MIX(29) PD_TF_MIX(16) PD_TF_MIX(24)
+    x0 += ks2; x1 += ks0 + 2u;
+    PD_TF_MIX(13) PD_TF_MIX(15) PD_TF_MIX(26) PD_TF_MIX(6)
+    x0 += ks0; x1 += ks1 + 3u;
+    PD_TF_MIX(17) PD_TF_MIX(29) PD_TF_MIX(16) PD_TF_MIX(24)
+    x0 += ks1; x1 += ks2 + 4u;
+    PD_TF_MIX(13) PD_TF_MIX(15) PD_TF_MIX(26) PD_TF_MIX(6)
+    x0 += ks2; x1 += ks0 + 5u;
+#undef PD_TF_MIX
+    pd_u32x2 out; out.a = x0; out.b = x1;
+    return out;
+}
+
+// random_bits(key, shape)[flat]: counter = (0, flat index); the two output
+// words are folded with xor into one 32-bit draw.
+PD_HD uint32_t pd_random_bits(uint32_t k0, uint32_t k1, uint32_t flat_index) {
+    pd_u32x2 r = pd_threefry2x32(k0, k1, 0u, flat_index);
+    return r.a ^ r.b;
+}
+
+// fold_in(key, data): counter = (0, data); both output words form the new key.
+PD_HD pd_u32x2 pd_fold_in(uint32_t k0, uint32_t k1, uint32_t data) {
+    return pd_threefry2x32(k0, k1, 0u, data);
+}
+
+// uniform [0, 1): keep the top 23 bits as a mantissa under exponent 0
+// (a float in [1, 2)), then subtract one.
+PD_HD float pd_bits_to_uniform(uint32_t bits) {
+    return pd_sub(pd_u2f((bits >> 9) | 0x3F800000u), 1.0f);
+}
+
+// ---------------------------------------------------------------------------
+// df32: value = hi + lo with |lo| <= ulp(hi)/2.
+// ---------------------------------------------------------------------------
+typedef struct pd_df32 { float hi, lo; } pd_df32;
+
+PD_HD pd_df32 pd_df_make(float hi, float lo) { pd_df32 r; r.hi = hi; r.lo = lo; return r; }
+PD_HD pd_df32 pd_df_from_float(float a) { return pd_df_make(a, 0.0f); }
+PD_HD float pd_df_to_float(pd_df32 a) { return pd_add(a.hi, a.lo); }
+
+// Knuth TwoSum: s + e == a + b exactly, no ordering assumption (6 flops).
+PD_HD pd_df32 pd_two_sum(float a, float b) {
+    float s = pd_add(a, b);
+    float bb = pd_sub(s, a);
+    float e = pd_add(pd_sub(a, pd_sub(s, bb)), pd_sub(b, bb));
+    return pd_df_make(s, e);
+}
+// Dekker FastTwoSum: exact when |a| >= |b| (3 flops).
+PD_HD pd_df32 pd_fast_two_sum(float a, float b) {
+    float s = pd_add(a, b);
+    float e = pd_sub(b, pd_sub(s, a));
+    return pd_df_make(s, e);
+}
+// TwoProd with FMA: p + e == a * b exactly (2 flops).
+PD_HD pd_df32 pd_two_prod(float a, float b) {
+    float p = pd_mul(a, b);
+    float e = pd_fma(a, b, -p);
+    return pd_df_make(p, e);
+}
+
+// Accurate df32 addition (both low-order words go through a TwoSum).
+PD_HD pd_df32 pd_df_add(pd_df32 a, pd_df32 b) {
+    pd_df32 s = pd_two_sum(a.hi, b.hi);
+    pd_df32 t = pd_two_sum(a.lo, b.lo);
+    s.lo = pd_add(s.lo, t.hi);
+    s = pd_fast_two_sum(s.hi, s.lo);
+    s.lo = pd_add(s.lo, t.lo);
+    return pd_fast_two_sum(s.hi, s.lo);
+}
+PD_HD pd_df32 pd_df_neg(pd_df32 a) { return pd_df_make(-a.hi, -a.lo); }
+PD_HD pd_df32 pd_df_sub(pd_df32 a, pd_df32 b) { return pd_df_add(a, pd_df_neg(b)); }
+
+PD_HD pd_df32 pd_df_mul(pd_df32 a, pd_df32 b) {
+    pd_df32 p = pd_two_prod(a.hi, b.hi);
+    p.lo = pd_fma(a.hi, b.lo, p.lo);
+    p.lo = pd_fma(a.lo, b.hi, p.lo);
+    return pd_fast_two_sum(p.hi, p.lo);
+}
+
+// df32 / df32: two quotient digits from IEEE float division, each followed by
+// an exact residual update, plus a third correction digit.
+PD_HD pd_df32 pd_df_div(pd_df32 a, pd_df32 b) {
+    float q1 = pd_div(a.hi, b.hi);
+    pd_df32 r = pd_df_sub(a, pd_df_mul(pd_df_from_float(q1), b));
+    float q2 = pd_div(r.hi, b.hi);
+    r = pd_df_sub(r, pd_df_mul(pd_df_from_float(q2), b));
+    float q3 = pd_div(r.hi, b.hi);
+    pd_df32 q = pd_fast_two_sum(q1, q2);
+    return pd_df_add(q, pd_df_from_float(q3));
+}
+
+// sqrt(df32): IEEE float sqrt as the seed, one Newton correction carried out
+// in df32:  r = s + (a - s*s) / (2 s).   a must be >= 0; sqrt(0) = 0.
+PD_HD pd_df32 pd_df_sqrt(pd_df32 a) {
+    float s = pd_sqrt(a.hi);
+    if (s == 0.0f) return pd_df_make(0.0f, 0.0f);
+    pd_df32 ss = pd_two_prod(s, s);
+    pd_df32 d = pd_df_sub(a, ss);
+    float corr = pd_div(d.hi, pd_add(s, s));
+    return pd_fast_two_sum(s, corr);
+}
+
+// ---------------------------------------------------------------------------
+// pd_powf: deterministic x**y for x >= 0.
+//   log2(x) is formed in df32 from x = 2^e * m, m in [sqrt(1/2), sqrt(2)],
+//   s = (m-1)/(m+1), log(m) = 2 s + 2 s^3/3 + ... ; the product y * log2(x)
+//   is split into an integer n and a fraction f, |f| <= 1/2, and 2^f is a
+//   degree-7 polynomial.  Measured against double-precision pow rounded to
+//   float the result is within 1 ulp over the tested domain.
+//   Domain rules: NaN in -> NaN; x < 0 -> NaN; y == 0 -> 1; x == 0 -> 0 (y>0)
+//   or +inf (y<0); x == +inf -> +inf (y>0) or 0 (y<0).
+// ---------------------------------------------------------------------------
+PD_HD float pd_exp2_scale(float r, int n) {
+    // r * 2^n for r in [1/2, 2] and n in [-160, 254].  Every multiply but the
+    // last is exact, so a subnormal result is rounded exactly once.
+    if (n > 127) {
+        r = pd_mul(r, pd_u2f(254u << 23));       // * 2^127
+        n -= 127;
+        if (n > 127) n = 127;
+    }
+    if (n < -126) {
+        if (n < -160) n = -160;
+        r = pd_mul(r, pd_u2f((uint32_t)(n + 64 + 127) << 23));  // * 2^(n+64), normal
+        n = -64;
+    }
+    return pd_mul(r, pd_u2f((uint32_t)(n + 127) << 23));
+}
+
+PD_HD float pd_powf(float x, float y) {
+    if (x != x || y != y) return x + y;
+    if (y == 0.0f) return 1.0f;
+    if (x < 0.0f) return pd_u2f(0x7FC00000u);
+    const float inf = pd_u2f(0x7F800000u);
+    if (x == 0.0f) return y > 0.0f ? 0.0f : inf;
+    if (x == inf) return y > 0.0f ? inf : 0.0f;
+    if (y == inf) return x > 1.0f ? inf : (x == 1.0f ? 1.0f : 0.0f);
+    if (y == -inf) return x > 1.0f ? 0.0f : (x == 1.0f ? 1.0f : inf);
+
+    uint32_t ix = pd_f2u(x);
+    int e = 0;
+    if (ix < 0x00800000u) {  // subnormal: scale up by 2^24 (exact)
+        ix = pd_f2u(pd_mul(x, 16777216.0f));
+        e = -24;
+    }
+    e += (int)(ix >> 23) - 127;
+    float m = pd_u2f((ix & 0x007FFFFFu) | 0x3F800000u);  // [1, 2)
+    if (m > 1.41421354f) { m = pd_mul(m, 0.5f); e += 1; }
+
+    // s = (m - 1) / (m + 1) as a df32 value.
+    float num = pd_sub(m, 1.0f);                 // exact
+    pd_df32 den = pd_two_sum(m, 1.0f);
+    float s_hi = pd_div(num, den.hi);
+    float res = pd_fma(-s_hi, den.hi, num);      // exact residual
+    res = pd_fma(-s_hi, den.lo, res);
+    float s_lo = pd_div(res, den.hi);
+
+    // log(m) = 2 s + s * q(z), z = s^2.
+    float z = pd_mul(s_hi, s_hi);
+    float q = 0.153846154f;                      // 2/13
+    q = pd_fma(q, z, 0.181818182f);              // 2/11
+    q = pd_fma(q, z, 0.222222222f);              // 2/9
+    q = pd_fma(q, z, 0.285714286f);              // 2/7
+    q = pd_fma(q, z, 0.4f);                      // 2/5
+    q = pd_fma(q, z, 0.666666667f);              // 2/3
+    q = pd_mul(q, z);
+    float tail = pd_fma(s_hi, q, pd_add(s_lo, s_lo));
+    pd_df32 L = pd_fast_two_sum(pd_add(s_hi, s_hi), tail);
+
+    // log2(m) = L * log2(e), log2(e) = 1.44269502162933349609375 + 1.925963033500011e-8
+    const float c_hi = 1.44269502f, c_lo = 1.92596303e-8f;
+    pd_df32 P = pd_two_prod(L.hi, c_hi);
+    P.lo = pd_fma(L.hi, c_lo, P.lo);
+    P.lo = pd_fma(L.lo, c_hi, P.lo);
+
+    // T = e + P
+    pd_df32 T = pd_two_sum((float)e, P.hi);
+    T.lo = pd_add(T.lo, P.lo);
+    T = pd_fast_two_sum(T.hi, T.lo);
+
+    // W = y * T
+    pd_df32 W = pd_two_prod(y, T.hi);
+    W.lo = pd_fma(y, T.lo, W.lo);
+
+    if (!(W.hi < 129.0f)) return inf;
+    if (!(W.hi > -151.0f)) return 0.0f;
+
+    float nf = floorf(pd_add(W.hi, 0.5f));
+    float f = pd_add(pd_sub(W.hi, nf), W.lo);
+    int n = (int)nf;
+
+    // 2^f - 1 = f * (ln2 + f * (ln2^2/2 + ...)), Taylor coefficients ln2^k / k!
+    float p = 1.52527338e-5f;                    // ln2^7/7!
+    p = pd_fma(p, f, 1.54035304e-4f);            // ln2^6/6!
+    p = pd_fma(p, f, 1.33335581e-3f);            // ln2^5/5!
+    p = pd_fma(p, f, 9.61812911e-3f);            // ln2^4/4!
+    p = pd_fma(p, f, 5.55041087e-2f);            // ln2^3/3!
+    p = pd_fma(p, f, 2.40226507e-1f);            // ln2^2/2!
+    p = pd_fma(p, f, 6.93147181e-1f);            // ln2
+    float r = pd_fma(p, f, 1.0f);
+    return pd_exp2_scale(r, n);
+}
+
+#endif  // PD_MATH_H_

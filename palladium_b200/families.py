@@ -1,0 +1,367 @@
+"""Kernel families: what takes the place of a Pallas kernel function.
+
+The reference traces an arbitrary Pallas function into a `KernelSpec` and emits
+MSL for it (src/palladium/trace.py:117-178, src/palladium/emit/core.py:383-466).
+This package has no emitter: the five integrator kernels are hand-written CUDA,
+and `cuda_call(kernel, ...)` takes a *family descriptor* as its `kernel`
+argument.  A descriptor names the family, carries the constants the reference
+kernels close over as module globals (DT, STEPS, tolerances, ...), and checks
+that the `grid` / `in_specs` / `out_specs` / `out_shape` of the call describe
+the launch that family performs -- the same keywords, with the same meaning, a
+user of the reference already writes for `metal_call`.
+
+`trace(call_kwargs, family, *args)` produces the `KernelSpec` analogue: name,
+grid, and one `BlockInfo` per operand.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+from collections.abc import Callable, Sequence
+from typing import Any
+
+import numpy as np
+
+from . import _native
+from .errors import DispatchError, TraceError, UnsupportedPrimitiveError
+
+__all__ = [
+    "BlockInfo",
+    "Family",
+    "KernelSpec",
+    "gbm_threefry",
+    "gray_scott",
+    "kepler_rk4_df32",
+    "lv_rk4",
+    "lv_rk4_df32",
+    "threefry_bits",
+    "trace",
+    "vdp_bs32",
+]
+
+F32 = np.dtype(np.float32)
+U32 = np.dtype(np.uint32)
+I32 = np.dtype(np.int32)
+F64 = np.dtype(np.float64)
+
+
+@dataclasses.dataclass(frozen=True)
+class BlockInfo:
+    """One operand of a traced call (src/palladium/trace.py:26-50)."""
+
+    block_shape: tuple[int, ...]
+    array_shape: tuple[int, ...]
+    dtype: np.dtype
+
+
+@dataclasses.dataclass(frozen=True)
+class KernelSpec:
+    """A validated call: the analogue of the reference's traced KernelSpec
+    (src/palladium/trace.py:53-80) with the family in place of a jaxpr."""
+
+    name: str
+    family: "Family"
+    grid: tuple[int, ...]
+    inputs: tuple[BlockInfo, ...]
+    outputs: tuple[BlockInfo, ...]
+    params: ctypes.Structure
+
+    @property
+    def num_programs(self) -> int:
+        return int(np.prod(self.grid)) if self.grid else 1
+
+
+@dataclasses.dataclass(frozen=True)
+class Family:
+    """A hand-written kernel family plus the constants of one problem.
+
+    `pallas_fn`, when given and JAX is installed, is the user's own Pallas
+    kernel function for the same computation; `.interpret` then runs it through
+    `pl.pallas_call(..., interpret=True)` exactly as the reference does."""
+
+    name: str
+    constants: dict[str, Any]
+    pallas_fn: Callable | None = None
+
+    @property
+    def family_id(self) -> int:
+        return _native.FAMILY_IDS[self.name]
+
+    def __call__(self, *refs):
+        raise UnsupportedPrimitiveError(
+            f"{self.name} is a hand-written CUDA kernel family, not a Pallas function; "
+            "pass it to palladium_b200.cuda_call instead of calling it"
+        )
+
+
+# ----------------------------------------------------------------------------- constructors
+def lv_rk4(dt: float = 0.01, steps: int = 500, pallas_fn: Callable | None = None) -> Family:
+    """Fixed-step RK4 Lotka-Volterra ensemble (examples/01_ode_ensembles.py:72-91).
+    Call signature: grid=(N,), six (N,) float32 inputs x0, y0, a, b, c, d,
+    two (N,) float32 outputs."""
+    return Family("lv_rk4", dict(dt=float(dt), steps=int(steps)), pallas_fn)
+
+
+def vdp_bs32(t1: float = 10.0, rtol: float = 1e-5, atol: float = 1e-7, dt0: float = 0.01,
+             max_steps: int = 6000, pcoeff: float = 0.4, icoeff: float = 0.3, safety: float = 0.9,
+             factor_min: float = 0.2, factor_max: float = 10.0, error_order: int = 3,
+             pallas_fn: Callable | None = None) -> Family:
+    """Adaptive Bogacki-Shampine 3(2) Van der Pol ensemble
+    (examples/02_adaptive_lockstep.py:69-171; defaults from :20-32).
+    grid=(N,), inputs x0, v0, mu.  The output layout follows `out_shape`:
+    six float32 (N,) arrays t, x, v, steps, rejected, real; five (without
+    `real`, tests/test_08_adaptive.py:33-142); or an (N, 2) float32 state plus
+    int32 accepted and rejected counts."""
+    return Family("vdp_bs32", dict(t1=float(t1), rtol=float(rtol), atol=float(atol), dt0=float(dt0),
+                                   max_steps=int(max_steps), pcoeff=float(pcoeff), icoeff=float(icoeff),
+                                   safety=float(safety), factor_min=float(factor_min),
+                                   factor_max=float(factor_max), error_order=int(error_order)), pallas_fn)
+
+
+def gbm_threefry(s0: float = 100.0, strike: float = 105.0, r: float = 0.03, sigma: float = 0.2, t: float = 1.0,
+                 steps: int = 256, output: str = "payoff", path_offset: int = 0,
+                 pallas_fn: Callable | None = None) -> Family:
+    """GBM European call paths with in-kernel Threefry (examples/03_sde_montecarlo.py:97-119;
+    defaults from :30-32).  grid=(N,), one (2,) uint32 input (key data), one (N,)
+    float32 output: the payoff max(S_T - K, 0) (`output="payoff"`, the reference)
+    or the terminal price S_T (`output="terminal"`).  An optional second output
+    of shape (2,) float64 receives (sum payoff, sum payoff^2)."""
+    if output not in ("payoff", "terminal"):
+        raise TraceError(f"gbm_threefry: output must be 'payoff' or 'terminal', got {output!r}")
+    return Family("gbm_threefry", dict(s0=float(s0), strike=float(strike), r=float(r), sigma=float(sigma),
+                                       t=float(t), steps=int(steps), output=output,
+                                       path_offset=int(path_offset)), pallas_fn)
+
+
+def gray_scott(du: float = 0.16, dv: float = 0.08, f: float = 0.035, k: float = 0.065, dt: float = 1.0,
+               steps: int = 1, halo: int = 0, pallas_fn: Callable | None = None) -> Family:
+    """Gray-Scott 5-point stencil (examples/04_reaction_diffusion.py:61-74; constants :35).
+    grid=(rows, cols), inputs u, v and outputs u', v' of shape (rows, cols)
+    float32.  `steps` > 1 runs that many steps inside one call with the fields
+    resident on the device (the reference's ping-pong loop, :99-107).
+    `halo` > 0 treats the arrays as a row slab of shape (rows + 2*halo, cols)
+    with ghost rows that the caller fills; at most `halo` steps per call."""
+    return Family("gray_scott", dict(du=float(du), dv=float(dv), f=float(f), k=float(k), dt=float(dt),
+                                     steps=int(steps), halo=int(halo)), pallas_fn)
+
+
+def lv_rk4_df32(dt: float = 0.01, steps: int = 500) -> Family:
+    """RK4 Lotka-Volterra in df32 compensated arithmetic
+    (examples/05_df32_precision.py:27-80).  Same signature as `lv_rk4`."""
+    return Family("lv_rk4_df32", dict(dt=float(dt), steps=int(steps)))
+
+
+def kepler_rk4_df32(dt: float = 1e-3, gm: float = 1.0, steps: int = 1000) -> Family:
+    """RK4 two-body orbits in df32.  grid=(N,), eight (N,) float32 inputs
+    (x, y, vx, vy as hi/lo pairs) and eight outputs of the same layout."""
+    return Family("kepler_rk4_df32", dict(dt=float(dt), gm=float(gm), steps=int(steps)))
+
+
+def threefry_bits(op: str = "bits", count: int = 1) -> Family:
+    """The RNG primitives on their own (src/palladium/emit/rules.py:168-201):
+    op "bits": (N,) uint32 = random_bits(key, (N,)); "uniform": (N,) float32;
+    "fold_in": inputs key and (M,) uint32 data, output (M, 2) uint32 key data;
+    "fold_uniform": (G, count) float32, row g = uniform(fold_in(key, g), (count,))."""
+    ops = {"bits": 0, "uniform": 1, "fold_in": 2, "fold_uniform": 3}
+    if op not in ops:
+        raise TraceError(f"threefry_bits: op must be one of {sorted(ops)}, got {op!r}")
+    return Family("threefry_bits", dict(op=op, op_code=ops[op], count=int(count)))
+
+
+# ----------------------------------------------------------------------------- tracing
+def _shape_dtype(x) -> tuple[tuple[int, ...], np.dtype]:
+    shape = getattr(x, "shape", None)
+    dtype = getattr(x, "dtype", None)
+    if shape is None or dtype is None:
+        arr = np.asarray(x)
+        shape, dtype = arr.shape, arr.dtype
+    return tuple(int(s) for s in shape), np.dtype(dtype)
+
+
+def _as_list(x) -> list:
+    if x is None:
+        return []
+    if isinstance(x, (list, tuple)):
+        return list(x)
+    return [x]
+
+
+def _check_specs(what: str, specs, expected_blocks: Sequence[tuple[tuple[int, ...], Callable]], grid) -> None:
+    """Validate in_specs / out_specs against the block shapes and index maps the
+    family implements.  A spec of None (or a missing list) is accepted: Pallas
+    then defaults to whole-array blocks, which the fixed kernels do not depend on."""
+    specs = _as_list(specs)
+    if not specs:
+        return
+    if len(specs) != len(expected_blocks):
+        raise TraceError(f"{what} has {len(specs)} entries, the kernel family takes {len(expected_blocks)}")
+    probes = [tuple(0 for _ in grid), tuple(max(g - 1, 0) for g in grid)]
+    for i, (spec, (block, index_map)) in enumerate(zip(specs, expected_blocks)):
+        if spec is None:
+            continue
+        got_block = getattr(spec, "block_shape", None)
+        if got_block is not None and tuple(int(b) for b in got_block) != tuple(block):
+            raise TraceError(f"{what}[{i}]: block shape {tuple(got_block)} is not the {tuple(block)} this family uses")
+        got_map = getattr(spec, "index_map", None)
+        if got_map is not None:
+            for probe in probes:
+                try:
+                    got = tuple(int(v) for v in got_map(*probe))
+                except Exception as exc:  # a map of the wrong arity, most likely
+                    raise TraceError(f"{what}[{i}]: index_map could not be evaluated at {probe}: {exc}") from None
+                want = tuple(int(v) for v in index_map(*probe))
+                if got != want:
+                    raise TraceError(f"{what}[{i}]: index_map{probe} = {got}, this family needs {want}")
+
+
+def _check_args(args, inputs: Sequence[BlockInfo]) -> None:
+    if not args:
+        return
+    if len(args) != len(inputs):
+        raise TraceError(f"kernel takes {len(inputs)} arrays, got {len(args)}")
+    for i, (a, info) in enumerate(zip(args, inputs)):
+        shape, dtype = _shape_dtype(a)
+        if shape != info.array_shape:
+            raise TraceError(f"argument {i}: shape {shape} does not match the {info.array_shape} implied by grid")
+        if dtype != info.dtype:
+            raise DispatchError(
+                f"argument {i}: dtype {dtype} does not match the traced {info.dtype}; cast explicitly"
+            )
+
+
+def _out_structs(out_shape) -> list[tuple[tuple[int, ...], np.dtype]]:
+    if out_shape is None:
+        raise TraceError("out_shape is required")
+    return [_shape_dtype(o) for o in _as_list(out_shape)]
+
+
+def _per_item(n: int):
+    return ((1,), lambda i: (i,))
+
+
+def trace(family: Family, call_kwargs: dict[str, Any], *args) -> KernelSpec:
+    """Validate a `pallas_call`-shaped call against a family; returns the spec.
+
+    Raises TraceError when grid / specs / out_shape / argument shapes do not
+    describe a launch of that family (the reference raises TraceError when a
+    pallas_call cannot be traced, src/palladium/trace.py:83-99,139-166)."""
+    if not isinstance(family, Family):
+        raise UnsupportedPrimitiveError(
+            "cuda_call needs a kernel family from palladium_b200.families (there is no "
+            f"Pallas-to-CUDA emitter); got {type(family).__name__}"
+        )
+    unknown = set(call_kwargs) - {"grid", "in_specs", "out_specs", "out_shape", "name", "interpret", "debug",
+                                  "input_output_aliases", "compiler_params", "cost_estimate", "grid_spec"}
+    if unknown:
+        raise TraceError(f"unsupported pallas_call keywords: {sorted(unknown)}")
+    if call_kwargs.get("grid_spec") is not None:
+        raise TraceError("grid_spec (scalar prefetch) is not supported; pass grid / in_specs / out_specs")
+    if call_kwargs.get("input_output_aliases"):
+        raise TraceError("input_output_aliases is not supported")
+    grid = call_kwargs.get("grid")
+    grid = (int(grid),) if isinstance(grid, (int, np.integer)) else tuple(int(g) for g in (grid or ()))
+    outs = _out_structs(call_kwargs.get("out_shape"))
+    c = family.constants
+    name = family.name
+
+    def vec(n, dtype=F32):
+        return BlockInfo((1,), (n,), dtype)
+
+    if name in ("lv_rk4", "lv_rk4_df32"):
+        if len(grid) != 1:
+            raise TraceError(f"{name}: grid must be (N,), got {grid}")
+        n = grid[0]
+        inputs = tuple(vec(n) for _ in range(6))
+        outputs = tuple(vec(n) for _ in range(2))
+        blocks_in = [_per_item(n)] * 6
+        blocks_out = [_per_item(n)] * 2
+        if name == "lv_rk4":
+            params = _native.LvRk4Params(c["dt"], c["steps"])
+        else:
+            params = _native.LvRk4Df32Params(c["dt"], c["steps"])
+    elif name == "vdp_bs32":
+        if len(grid) != 1:
+            raise TraceError(f"{name}: grid must be (N,), got {grid}")
+        n = grid[0]
+        inputs = tuple(vec(n) for _ in range(3))
+        blocks_in = [_per_item(n)] * 3
+        if len(outs) == 6:
+            layout, outputs, blocks_out = 0, tuple(vec(n) for _ in range(6)), [_per_item(n)] * 6
+        elif len(outs) == 5:
+            layout, outputs, blocks_out = 1, tuple(vec(n) for _ in range(5)), [_per_item(n)] * 5
+        elif len(outs) == 3:
+            layout = 2
+            outputs = (BlockInfo((1, 2), (n, 2), F32), vec(n, I32), vec(n, I32))
+            blocks_out = [((1, 2), lambda i: (i, 0)), _per_item(n), _per_item(n)]
+        else:
+            raise TraceError(f"{name}: out_shape must list 6, 5 or 3 outputs, got {len(outs)}")
+        params = _native.VdpBs32Params(c["t1"], c["rtol"], c["atol"], c["dt0"], c["pcoeff"], c["icoeff"],
+                                       c["safety"], c["factor_min"], c["factor_max"], c["error_order"],
+                                       c["max_steps"], layout)
+    elif name == "gbm_threefry":
+        if len(grid) != 1:
+            raise TraceError(f"{name}: grid must be (N,), got {grid}")
+        n = grid[0]
+        inputs = (BlockInfo((2,), (2,), U32),)
+        blocks_in = [((2,), lambda i: (0,))]
+        outputs = (vec(n),)
+        blocks_out = [_per_item(n)]
+        if len(outs) == 2:
+            outputs = outputs + (BlockInfo((2,), (2,), F64),)
+            blocks_out = blocks_out + [((2,), lambda i: (0,))]
+        elif len(outs) != 1:
+            raise TraceError(f"{name}: out_shape must list 1 or 2 outputs, got {len(outs)}")
+        params = _native.GbmParams(c["s0"], c["strike"], c["r"], c["sigma"], c["t"], c["steps"], c["path_offset"],
+                                   0 if c["output"] == "payoff" else 1)
+    elif name == "gray_scott":
+        if len(grid) != 2:
+            raise TraceError(f"{name}: grid must be (rows, cols), got {grid}")
+        rows, cols = grid
+        shape = (rows + 2 * c["halo"], cols)
+        inputs = tuple(BlockInfo(shape, shape, F32) for _ in range(2))
+        outputs = tuple(BlockInfo(shape, shape, F32) for _ in range(2))
+        blocks_in = [(shape, lambda i, j: (0, 0))] * 2
+        blocks_out = [(shape, lambda i, j: (0, 0))] * 2
+        params = _native.GrayScottParams(c["du"], c["dv"], c["f"], c["k"], c["dt"], c["steps"], rows, cols, c["halo"])
+    elif name == "kepler_rk4_df32":
+        if len(grid) != 1:
+            raise TraceError(f"{name}: grid must be (N,), got {grid}")
+        n = grid[0]
+        inputs = tuple(vec(n) for _ in range(8))
+        outputs = tuple(vec(n) for _ in range(8))
+        blocks_in = [_per_item(n)] * 8
+        blocks_out = [_per_item(n)] * 8
+        params = _native.KeplerRk4Df32Params(c["dt"], c["gm"], c["steps"])
+    elif name == "threefry_bits":
+        if len(grid) != 1:
+            raise TraceError(f"{name}: grid must be (N,), got {grid}")
+        n = grid[0]
+        key = BlockInfo((2,), (2,), U32)
+        op = c["op"]
+        if op == "bits":
+            inputs, outputs = (key,), (vec(n, U32),)
+        elif op == "uniform":
+            inputs, outputs = (key,), (vec(n),)
+        elif op == "fold_in":
+            inputs, outputs = (key, vec(n, U32)), (BlockInfo((1, 2), (n, 2), U32),)
+        else:
+            inputs, outputs = (key,), (BlockInfo((1, c["count"]), (n, c["count"]), F32),)
+        blocks_in = blocks_out = None
+        params = _native.ThreefryParams(c["op_code"], c["count"])
+    else:
+        raise UnsupportedPrimitiveError(f"no CUDA kernel family named {name!r}")
+
+    if len(outs) != len(outputs):
+        raise TraceError(f"{name}: out_shape lists {len(outs)} outputs, the kernel family produces {len(outputs)}")
+    for i, ((shape, dtype), info) in enumerate(zip(outs, outputs)):
+        if shape != info.array_shape or dtype != info.dtype:
+            raise TraceError(
+                f"{name}: out_shape[{i}] is {shape} {dtype}, the kernel family produces "
+                f"{info.array_shape} {info.dtype} for grid {grid}"
+            )
+    if blocks_in is not None:
+        _check_specs("in_specs", call_kwargs.get("in_specs"), blocks_in, grid)
+        _check_specs("out_specs", call_kwargs.get("out_specs"), blocks_out, grid)
+    _check_args(args, inputs)
+    return KernelSpec(name=f"palladium_{name}", family=family, grid=grid, inputs=inputs, outputs=outputs, params=params)

@@ -1,0 +1,288 @@
+"""GPU parity: each CUDA kernel family against the CPU oracle on the same
+seeded inputs, through the public call (which reaches the GPU via the C ABI).
+
+Bars: bit-exact for RNG bits, integer step counts and every SAFE-mode kernel
+whose arithmetic is IEEE +,-,*,/,sqrt,fma; rtol 1e-5 for float32 states in
+RELAXED / FAST; the reference's own looser bars where it states one."""
+
+import numpy as np
+import pytest
+
+import oracle
+import palladium_b200 as pd
+from palladium_b200 import workloads as W
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+SAFE, RELAXED, FAST = pd.MathMode.SAFE, pd.MathMode.RELAXED, pd.MathMode.FAST
+
+
+# ------------------------------------------------------------------ RNG: bit-exact
+@pytest.mark.parametrize("n", [1, 16, 1000, 100_003])
+def test_random_bits_exact(n):
+    key = np.array([0x12345678, 0x9ABCDEF0], np.uint32)
+    got = H.threefry_solver("bits", n)(key)
+    np.testing.assert_array_equal(got, oracle.random_bits(key, n))
+
+
+def test_uniform_exact():
+    key = W.gbm_key(1234)
+    got = H.threefry_solver("uniform", 64)(key)
+    np.testing.assert_array_equal(got, oracle.uniform(key, 64))
+    assert got.min() >= 0.0 and got.max() < 1.0
+
+
+def test_fold_in_exact():
+    key = W.gbm_key(99)
+    data = np.array([17, 0, 1, 0xFFFFFFFF, 123456789], np.uint32)
+    got = H.threefry_solver("fold_in", data.size)(key, data)
+    np.testing.assert_array_equal(got, oracle.fold_in(key, data))
+
+
+def test_per_thread_independent_streams():
+    # tests/test_10_random_bits.py:78-108 in the reference
+    key = W.gbm_key(7)
+    got = H.threefry_solver("fold_uniform", 8, count=4)(key)
+    np.testing.assert_array_equal(got, oracle.fold_uniform(key, 8, 4))
+    assert len({tuple(row) for row in got}) == 8
+
+
+# ------------------------------------------------------------------ RK4 Lotka-Volterra
+@pytest.mark.parametrize("n", [1, 31, 32, 33, 4097, 100_000])
+def test_lv_rk4_safe_bit_exact(n):
+    args = W.lotka_volterra_ensemble(n)
+    got_x, got_y = H.lv_solver(n, steps=300, math_mode=SAFE)(*args)
+    want_x, want_y = oracle.lv_rk4(*args, dt=0.01, steps=300)
+    np.testing.assert_array_equal(got_x, want_x)
+    np.testing.assert_array_equal(got_y, want_y)
+
+
+@pytest.mark.parametrize("items", [1, 2, 4])
+def test_lv_rk4_items_per_thread_agree(items):
+    from palladium_b200 import _native
+
+    n = 10_007
+    args = W.lotka_volterra_ensemble(n)
+    _native.set_tuning("lv_items_per_thread", items)
+    try:
+        got = H.lv_solver(n, steps=200, math_mode=SAFE)(*args)
+    finally:
+        _native.set_tuning("lv_items_per_thread", 0)
+    want = oracle.lv_rk4(*args, dt=0.01, steps=200)
+    np.testing.assert_array_equal(got[0], want[0])
+    np.testing.assert_array_equal(got[1], want[1])
+
+
+@pytest.mark.parametrize("mode,rtol", [(RELAXED, 1e-5), (FAST, 1e-5)])
+def test_lv_rk4_config_relaxed_fast(mode, rtol):
+    """The benchmark configuration: N = 100 000, dt = 0.01, 1000 steps."""
+    n = 100_000
+    args = W.lotka_volterra_ensemble(n)
+    got_x, got_y = H.lv_solver(n, steps=1000, math_mode=mode)(*args)
+    want_x, want_y = oracle.lv_rk4(*args, dt=0.01, steps=1000)
+    np.testing.assert_allclose(got_x, want_x, rtol=rtol, atol=1e-6)
+    np.testing.assert_allclose(got_y, want_y, rtol=rtol, atol=1e-6)
+
+
+def test_lv_rk4_matches_interpret_like_reference(rng, interpret_provider):
+    # tests/test_06_capstone_rk4.py:66-76: default (FAST) mode vs interpret
+    n = 512
+    f = H.lv_solver(n)
+    args = (rng.uniform(0.8, 1.2, n).astype(np.float32), rng.uniform(0.8, 1.2, n).astype(np.float32),
+            rng.uniform(0.9, 1.3, n).astype(np.float32), rng.uniform(0.3, 0.5, n).astype(np.float32),
+            rng.uniform(0.08, 0.12, n).astype(np.float32), rng.uniform(0.3, 0.5, n).astype(np.float32))
+    got_x, got_y = f(*args)
+    want_x, want_y = f.interpret(*args)
+    np.testing.assert_allclose(got_x, want_x, rtol=1e-3, atol=1e-5)
+    np.testing.assert_allclose(got_y, want_y, rtol=1e-3, atol=1e-5)
+
+
+# ------------------------------------------------------------------ adaptive BS3(2)
+VDP_CFG = dict(t1=20.0, rtol=1e-6, atol=1e-8, dt0=1e-3, max_steps=100_000)
+
+
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("n", [1, 33, 1000])
+def test_vdp_safe_counts_bit_exact(n, variant):
+    """SAFE shares every float operation (pow included) with the oracle, which
+    runs the full max_steps loop: state and all three counters are identical."""
+    from palladium_b200 import _native
+
+    x0, v0, mu = W.van_der_pol_ensemble(n)
+    _native.set_tuning("vdp_variant", variant)
+    try:
+        got = H.vdp_solver(n, outputs=6, math_mode=SAFE, **VDP_CFG)(x0, v0, mu)
+    finally:
+        _native.set_tuning("vdp_variant", 1)
+    want = oracle.vdp_bs32(x0, v0, mu, pow="pd", **VDP_CFG)
+    for g, w, name in zip(got, want, ("t", "x", "v", "steps", "rejected", "real")):
+        np.testing.assert_array_equal(g, w, err_msg=name)
+    assert np.all(got[0] == 20.0)
+    assert np.std(got[5]) > 0  # adaptivity is per trajectory
+
+
+def test_vdp_config_layout_int_counts():
+    n = 777
+    x0, v0, mu = W.van_der_pol_ensemble(n)
+    state, accepted, rejected = H.vdp_solver(n, outputs=3, math_mode=SAFE, **VDP_CFG)(x0, v0, mu)
+    want = oracle.vdp_bs32(x0, v0, mu, pow="pd", **VDP_CFG)
+    assert state.shape == (n, 2) and accepted.dtype == np.int32 and rejected.dtype == np.int32
+    np.testing.assert_array_equal(state[:, 0], want[1])
+    np.testing.assert_array_equal(state[:, 1], want[2])
+    np.testing.assert_array_equal(accepted, want[5].astype(np.int32))
+    np.testing.assert_array_equal(rejected, want[4].astype(np.int32))
+
+
+def test_vdp_relaxed_matches_interpret_like_reference(rng, interpret_provider):
+    # tests/test_08_adaptive.py:174-189: RELAXED vs interpret on a mild ensemble
+    n = 256
+    f = H.vdp_solver(n, outputs=5)
+    mu = rng.uniform(0.5, 2.0, n).astype(np.float32)
+    x0, v0 = np.full(n, 2.0, np.float32), np.zeros(n, np.float32)
+    got = f(x0, v0, mu)
+    want = oracle.vdp_bs32(x0, v0, mu, pow="libm")
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(got[1], want[1], rtol=1e-3, atol=1e-4)
+    np.testing.assert_allclose(got[2], want[2], rtol=1e-3, atol=1e-4)
+    np.testing.assert_allclose(got[3], want[3], rtol=0, atol=20)
+    np.testing.assert_allclose(got[4], want[4], rtol=0, atol=20)
+
+
+def test_vdp_reaches_t1_with_stiff_members(rng):
+    # tests/test_08_adaptive.py:192-199
+    n = 256
+    mu = rng.uniform(0.5, 2.0, n).astype(np.float32)
+    k = int(n * 0.02)
+    mu[rng.choice(n, k, replace=False)] = rng.uniform(300.0, 500.0, k).astype(np.float32)
+    got_t, *_ = H.vdp_solver(n, outputs=5)(np.full(n, 2.0, np.float32), np.zeros(n, np.float32), mu)
+    np.testing.assert_allclose(got_t, 10.0, rtol=0, atol=1e-4)
+
+
+# ------------------------------------------------------------------ GBM
+GBM_CFG = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=252)
+
+
+@pytest.mark.parametrize("mode,rtol", [(SAFE, 1e-5), (RELAXED, 1e-5), (FAST, 1e-4)])
+def test_gbm_terminal_prices(mode, rtol):
+    n = 1 << 14
+    key = W.gbm_key(0)
+    got = H.gbm_solver(n, math_mode=mode, output="terminal", **GBM_CFG)(key)
+    want, _ = oracle.gbm(key, n, **GBM_CFG)
+    np.testing.assert_allclose(got, want, rtol=rtol)
+
+
+def test_gbm_sums_and_black_scholes():
+    n = 1 << 20
+    key = W.gbm_key(0)
+    payoff, sums = H.gbm_solver(n, with_sums=True, **GBM_CFG)(key)
+    p64 = payoff.astype(np.float64)
+    np.testing.assert_allclose(sums[0], p64.sum(), rtol=1e-12)
+    np.testing.assert_allclose(sums[1], (p64 * p64).sum(), rtol=1e-12)
+    disc = np.exp(-GBM_CFG["r"] * GBM_CFG["t"])
+    price = disc * sums[0] / n
+    stderr = disc * np.sqrt((sums[1] / n - (sums[0] / n) ** 2) / n)
+    exact = oracle.black_scholes_call(100.0, 100.0, 1.0, 0.05, 0.2)
+    assert abs(price - exact) < 5 * stderr  # examples/03_sde_montecarlo.py:146
+
+
+def test_gbm_path_offset_is_global_index():
+    key = W.gbm_key(3)
+    whole = H.gbm_solver(4096, output="terminal", math_mode=SAFE, **GBM_CFG)(key)
+    part = H.gbm_solver(1024, output="terminal", math_mode=SAFE, path_offset=2048, **GBM_CFG)(key)
+    np.testing.assert_array_equal(part, whole[2048:3072])
+
+
+# ------------------------------------------------------------------ Gray-Scott
+@pytest.mark.parametrize("shape", [(32, 32), (30, 50), (64, 128), (96, 256), (33, 132), (256, 1024)])
+@pytest.mark.parametrize("steps", [1, 2, 7])
+def test_gray_scott_safe_bit_exact(shape, steps):
+    rows, cols = shape
+    rng = np.random.default_rng(5)
+    u = (1.0 - 0.5 * rng.random(shape)).astype(np.float32)
+    v = (0.25 * rng.random(shape)).astype(np.float32)
+    got_u, got_v = H.gs_solver(rows, cols, math_mode=SAFE, steps=steps)(u, v)
+    want_u, want_v = oracle.gray_scott(u, v, steps=steps)
+    np.testing.assert_array_equal(got_u, want_u)
+    np.testing.assert_array_equal(got_v, want_v)
+
+
+def test_gray_scott_patches_cross_the_seam():
+    size = 256
+    u, v = W.gray_scott_initial_state(size, seed=11, patches=8, patch=32)
+    got_u, got_v = H.gs_solver(size, size, math_mode=SAFE, steps=50)(u, v)
+    want_u, want_v = oracle.gray_scott(u, v, steps=50)
+    np.testing.assert_array_equal(got_u, want_u)
+    np.testing.assert_array_equal(got_v, want_v)
+
+
+@pytest.mark.parametrize("mode", [RELAXED, FAST])
+def test_gray_scott_relaxed_fast(mode):
+    size = 256
+    u, v = W.gray_scott_initial_state(size, seed=11, patches=8)
+    got_u, got_v = H.gs_solver(size, size, math_mode=mode, steps=100)(u, v)
+    want_u, want_v = oracle.gray_scott(u, v, steps=100)
+    np.testing.assert_allclose(got_u, want_u, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(got_v, want_v, rtol=1e-5, atol=1e-6)
+
+
+def test_gray_scott_slab_with_halo_matches_periodic():
+    """A row slab with k ghost rows advanced k steps equals the same rows of the
+    periodic grid advanced k steps."""
+    rows, cols, k = 64, 128, 4
+    rng = np.random.default_rng(9)
+    u = (1.0 - 0.5 * rng.random((rows, cols))).astype(np.float32)
+    v = (0.25 * rng.random((rows, cols))).astype(np.float32)
+    want_u, want_v = oracle.gray_scott(u, v, steps=k)
+    lo, hi = 16, 48  # owned rows of this slab
+    idx = np.arange(lo - k, hi + k) % rows
+    got_u, got_v = H.gs_solver(hi - lo, cols, math_mode=SAFE, steps=k, halo=k)(u[idx], v[idx])
+    np.testing.assert_array_equal(got_u[k:-k], want_u[lo:hi])
+    np.testing.assert_array_equal(got_v[k:-k], want_v[lo:hi])
+
+
+# ------------------------------------------------------------------ df32
+def test_lv_df32_bit_exact_and_more_accurate():
+    n = 4097
+    args = W.lotka_volterra_ensemble(n)
+    got_x, got_y = H.lv_solver(n, steps=500, df32=True, math_mode=SAFE)(*args)
+    want_x, want_y = oracle.lv_rk4_df32(*args, dt=0.01, steps=500)
+    np.testing.assert_array_equal(got_x, want_x)
+    np.testing.assert_array_equal(got_y, want_y)
+    # examples/05_df32_precision.py:197: df32 beats plain FAST float32 against float64.
+    # The float64 truth uses the same float32-rounded dt the df32 kernel receives.
+    ref_x, ref_y = oracle.lv_rk4_f64(*args, dt=float(np.float32(0.01)), steps=500)
+    fast_x, fast_y = H.lv_solver(n, steps=500, math_mode=FAST)(*args)
+    err_df = max(np.max(np.abs(got_x - ref_x)), np.max(np.abs(got_y - ref_y)))
+    err_fast = max(np.max(np.abs(fast_x - ref_x)), np.max(np.abs(fast_y - ref_y)))
+    assert err_df < err_fast
+
+
+@pytest.mark.parametrize("mode", [SAFE, FAST])
+def test_lv_df32_is_math_mode_invariant(mode):
+    n = 257
+    args = W.lotka_volterra_ensemble(n)
+    got = H.lv_solver(n, steps=100, df32=True, math_mode=mode)(*args)
+    want = oracle.lv_rk4_df32(*args, dt=0.01, steps=100)
+    np.testing.assert_array_equal(got[0], want[0])
+
+
+def test_kepler_df32_bit_exact_and_error_no_worse_than_oracle():
+    n, steps, dt = 2048, 2000, 1e-3
+    state64, pairs = W.kepler_ensemble(n)
+    got = H.kepler_solver(n, dt=dt, steps=steps)(*pairs)
+    want = oracle.kepler_rk4_df32(pairs, dt=dt, steps=steps)
+    for g, w in zip(got, want):
+        np.testing.assert_array_equal(g, w)
+    truth = oracle.kepler_rk4_f64(state64, dt=dt, steps=steps)
+    got64 = np.stack([W.join_df32(got[2 * i], got[2 * i + 1]) for i in range(4)], axis=1)
+    want64 = np.stack([W.join_df32(want[2 * i], want[2 * i + 1]) for i in range(4)], axis=1)
+    err_gpu = np.max(np.hypot(got64[:, 0] - truth[:, 0], got64[:, 1] - truth[:, 1]))
+    err_cpu = np.max(np.hypot(want64[:, 0] - truth[:, 0], want64[:, 1] - truth[:, 1]))
+    assert err_gpu <= err_cpu
+    f32 = oracle.kepler_rk4_f32(state64.astype(np.float32), dt=dt, steps=steps)
+    err_f32 = np.max(np.hypot(f32[:, 0] - truth[:, 0], f32[:, 1] - truth[:, 1]))
+    assert err_gpu < err_f32 * 1e-3
+    drift = np.abs(W.kepler_energy(got64) - W.kepler_energy(state64)) / np.abs(W.kepler_energy(state64))
+    drift_truth = np.abs(W.kepler_energy(truth) - W.kepler_energy(state64)) / np.abs(W.kepler_energy(state64))
+    assert np.max(np.abs(drift - drift_truth)) < 1e-9
