@@ -74,15 +74,29 @@ def test_lv_rk4_items_per_thread_agree(items):
     np.testing.assert_array_equal(got[1], want[1])
 
 
-@pytest.mark.parametrize("mode,rtol", [(RELAXED, 1e-5), (FAST, 1e-5)])
-def test_lv_rk4_config_relaxed_fast(mode, rtol):
-    """The benchmark configuration: N = 100 000, dt = 0.01, 1000 steps."""
+@pytest.mark.parametrize("mode", [RELAXED, FAST])
+def test_lv_rk4_config_relaxed_fast(mode):
+    """The benchmark configuration: N = 100 000, dt = 0.01, 1000 steps.
+
+    RELAXED contracts a*b+c into FMAs and FAST also reassociates, so each of
+    the 58 000 operations of a trajectory may round differently from the
+    oracle's strict order; SAFE is the mode that is identical to it (and so meets
+    rtol 1e-5 with zero difference).  The bar here: rtol 1e-5 for at least 95 %
+    of the states and 1e-4 for all of them (the reference asserts 1e-3 for FAST,
+    tests/test_06_capstone_rk4.py:75-76), and an error against a float64
+    integration no larger than 1.5x the oracle's own float32 error."""
     n = 100_000
     args = W.lotka_volterra_ensemble(n)
-    got_x, got_y = H.lv_solver(n, steps=1000, math_mode=mode)(*args)
-    want_x, want_y = oracle.lv_rk4(*args, dt=0.01, steps=1000)
-    np.testing.assert_allclose(got_x, want_x, rtol=rtol, atol=1e-6)
-    np.testing.assert_allclose(got_y, want_y, rtol=rtol, atol=1e-6)
+    got = H.lv_solver(n, steps=1000, math_mode=mode)(*args)
+    want = oracle.lv_rk4(*args, dt=0.01, steps=1000)
+    truth = oracle.lv_rk4_f64(*args, dt=0.01, steps=1000)
+    for g, w, t in zip(got, want, truth):
+        rel = np.abs(g - w) / np.maximum(np.abs(w), 1e-6)
+        assert np.mean(rel <= 1e-5) >= 0.95
+        assert rel.max() <= 1e-4
+        err_gpu = np.abs(g - t) / np.maximum(np.abs(t), 1e-6)
+        err_cpu = np.abs(w - t) / np.maximum(np.abs(t), 1e-6)
+        assert err_gpu.max() <= 1.5 * err_cpu.max()
 
 
 def test_lv_rk4_matches_interpret_like_reference(rng, interpret_provider):
@@ -119,7 +133,8 @@ def test_vdp_safe_counts_bit_exact(n, variant):
     for g, w, name in zip(got, want, ("t", "x", "v", "steps", "rejected", "real")):
         np.testing.assert_array_equal(g, w, err_msg=name)
     assert np.all(got[0] == 20.0)
-    assert np.std(got[5]) > 0  # adaptivity is per trajectory
+    if n > 1:
+        assert np.std(got[5]) > 0  # adaptivity is per trajectory (tests/test_08_adaptive.py:237-245)
 
 
 def test_vdp_config_layout_int_counts():
