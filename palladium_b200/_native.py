@@ -274,3 +274,4 @@ def measure_int32_alu_peak() -> float:
 
 def last_kernel_ms() -> float:
     return float(library().pd_last_kernel_ms())
+

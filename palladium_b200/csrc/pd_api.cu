@@ -481,7 +481,7 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             a.xo = (float*)out[0]; a.yo = (float*)out[1];
             a.n = n; a.steps = (int)p->steps;
             a.h_half = (float)(0.5 * p->dt); a.h_full = (float)p->dt;
-            a.h_sixth = (float)(p->dt / 6.0); a.h_third = (float)(p->dt / 3.0);
+            a.h_sixth = (float)(p->dt / 6.0);
             PD_CUDA_TRY(mt->lv_rk4(a, (int)plan.items, b, st));
             break;
         }

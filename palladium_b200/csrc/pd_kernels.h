@@ -15,7 +15,7 @@ struct PdLvArgs {
     float *xo, *yo;
     int64_t n;
     int steps;
-    float h_half, h_full, h_sixth, h_third;
+    float h_half, h_full, h_sixth;
 };
 
 struct PdVdpArgs {
