@@ -201,6 +201,28 @@ PD_API int pd_measure_int32_alu_peak(double* ops_per_s, char* err, size_t err_ca
  * pd_set_tuning("time_kernels", 1); it adds an event pair and a synchronise. */
 PD_API double pd_last_kernel_ms(void);
 
+/* Multi-step Gray-Scott on DEVICE buffers that allocates no device memory.
+ * No counterpart in the reference (its stepping loop lets metal-runtime
+ * allocate, examples/04_reaction_diffusion.py:92-98): it is for hosts that
+ * cannot let this library call cudaMalloc -- a process whose runtime reserved
+ * the GPU memory pool up front (XLA with preallocation, which is where the FFI
+ * handler runs), or a fixed-budget stepping loop that cannot take the
+ * device-wide synchronisation of cudaMalloc / cudaFree.
+ *   Same arithmetic, parameters and buffer layout as
+ *   pd_launch(PD_FAMILY_GRAY_SCOTT, ...); u, v are inputs, uo, vo outputs, each
+ *   (rows + 2*halo) x cols float32.  The ping-pong fields of a call with
+ *   steps >= 2 live in a fixed 8 MiB array inside the library image, held by
+ *   every GPU the library is used on until the process exits.
+ *   Limit: (rows + 2*halo) * cols <= 1 048 576 cells (2^20); larger calls return
+ *   PD_ERR_INVALID_ARGUMENT.  All calls on a device share that array: calls
+ *   whose kernels overlap on the GPU race on it, so order them on one stream.
+ *   Nothing in the array needs clearing between calls.  The first call on a
+ *   device resolves the array's address (cudaGetSymbolAddress); make it with
+ *   that device current and before beginning any stream capture. */
+PD_API int pd_gray_scott_static(const pd_gray_scott_params* params, int math_mode,
+                                const void* u, const void* v, void* uo, void* vo,
+                                void* cuda_stream, char* err, size_t err_cap);
+
 #ifdef __cplusplus
 }
 #endif

@@ -48,6 +48,7 @@ EXPORTED_SYMBOLS = (
     "pd_measure_fp32_fma_peak",
     "pd_measure_int32_alu_peak",
     "pd_last_kernel_ms",
+    "pd_gray_scott_static",
 )
 
 FAMILY_IDS = {
@@ -140,6 +141,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pd_measure_int32_alu_peak.argtypes = [ctypes.POINTER(_dbl), cp, sz]
     lib.pd_last_kernel_ms.restype = _dbl
     lib.pd_last_kernel_ms.argtypes = []
+    lib.pd_gray_scott_static.restype = ci
+    lib.pd_gray_scott_static.argtypes = [ctypes.POINTER(GrayScottParams), ci, vp, vp, vp, vp, vp, cp, sz]
 
 
 def library() -> ctypes.CDLL:
@@ -275,3 +278,13 @@ def measure_int32_alu_peak() -> float:
 def last_kernel_ms() -> float:
     return float(library().pd_last_kernel_ms())
 
+
+def gray_scott_static(params: GrayScottParams, math_mode: int, u: int, v: int, uo: int, vo: int,
+                      stream: int = 0) -> None:
+    """pd_gray_scott_static on device pointers: the multi-step stencil with its
+    ping-pong fields in the library's fixed 8 MiB array instead of allocated
+    scratch (at most 2^20 cells per call; calls on one device must not overlap)."""
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_gray_scott_static(ctypes.byref(params), math_mode, u, v, uo, vo, stream or None, err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)

@@ -76,6 +76,8 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         jobs.append(([nvcc, *ARCH, *COMMON, *flags, *extra, "-c", str(CSRC / "pd_kernels.cu"), "-o", str(obj)], obj))
     api_obj = BUILD_DIR / "pd_api.o"
     jobs.append(([nvcc, *ARCH, *COMMON, "-c", str(CSRC / "pd_api.cu"), "-o", str(api_obj)], api_obj))
+    noalloc_obj = BUILD_DIR / "pd_noalloc.o"
+    jobs.append(([nvcc, *ARCH, *COMMON, "-c", str(CSRC / "pd_noalloc.cu"), "-o", str(noalloc_obj)], noalloc_obj))
     with ThreadPoolExecutor(max_workers=len(jobs)) as pool:
         list(pool.map(lambda job: _run(job[0], verbose), jobs))
     link = [nvcc, *ARCH, "-shared", "-o", str(LIBRARY), *[str(obj) for _, obj in jobs]]
