@@ -1,0 +1,299 @@
+"""Timing of the kernel families other than the headline RK4 ensemble.
+
+`quick_summary()` measures each family once at a reduced, stated size with the
+inputs resident on the device (CUDA events on the launch stream) and returns a
+dict that `bench.py` embeds in its JSON line under "families".
+`run(...)` makes one family the benchmark's main workload
+(`bench.py --workload vdp_bs32|gbm|gray_scott|kepler_df32`), one rank per GPU.
+
+Algorithmic costs used for the roofline fractions:
+  adaptive BS3(2): one attempt = 97 float operations + 2 pow + 3 divisions
+      (counted from the kernel body; stall iterations are not attempts);
+  GBM: one path-step = 4 Threefry-2x32-20 blocks = 4 x (20 rounds x 3 + 5 x 3 + 2)
+      = 308 32-bit integer operations as written in the specification, plus
+      log, sqrt, cos, exp;
+  Gray-Scott: one cell-step = 16 bytes (read u, v; write u, v);
+  df32: one trajectory-step counted from pd_math.h (see DF32_FLOPS).
+"""
+
+from __future__ import annotations
+
+import json
+import time
+
+import numpy as np
+
+VDP_FLOPS_PER_ATTEMPT = 97
+GBM_INT_OPS_PER_PATH_STEP = 4 * (20 * 3 + 5 * 3 + 2)
+GS_BYTES_PER_CELL_STEP = 16
+# float operations per df32 primitive (pd_math.h), an FMA counted as 2: two_sum 6, fast_two_sum 3, two_prod 3
+DF_ADD, DF_MUL = 6 + 6 + 1 + 3 + 1 + 3, 3 + 2 + 2 + 3
+DF_DIV = 3 + 2 * (DF_MUL + DF_ADD) + 3 + DF_ADD
+DF_SQRT = 1 + 3 + DF_ADD + 1 + 1 + 3
+# LV: 4 rhs x (5 mul + 2 sub) + 3 advances x 2 x (mul + add) + combine 2 x (2 mul + 3 add) + final advance 2 x (mul + add)
+DF32_LV_FLOPS = 4 * (5 * DF_MUL + 2 * DF_ADD) + 3 * 2 * (DF_MUL + DF_ADD) + 2 * (2 * DF_MUL + 3 * DF_ADD) + 2 * (DF_MUL + DF_ADD)
+# Kepler rhs: 2 mul + add, sqrt, mul, div, 2 mul  (negation is free)
+_KEP_RHS = 2 * DF_MUL + DF_ADD + DF_SQRT + DF_MUL + DF_DIV + 2 * DF_MUL
+DF32_KEPLER_FLOPS = 4 * _KEP_RHS + 3 * 4 * (DF_MUL + DF_ADD) + 4 * (2 * DF_MUL + 3 * DF_ADD) + 4 * (DF_MUL + DF_ADD)
+HBM_PEAK_FALLBACK_GBS = 6650.0
+
+
+def _hbm_peak_gbs() -> tuple[float, str]:
+    from pathlib import Path
+
+    path = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(path.read_text())["hbm_gbs"]), "of measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return HBM_PEAK_FALLBACK_GBS, "of fallback (6.65 TB/s)"
+
+
+def _time(fn, warmup: int, iters: int) -> float:
+    """Average milliseconds per call of fn(), CUDA events on the current stream."""
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def _shaped(shape, dtype=np.float32):
+    from . import pl
+
+    return pl.ShapeDtypeStruct(shape, dtype)
+
+
+# ----------------------------------------------------------------------------- per family
+def bench_vdp(n: int, math_mode="relaxed", warmup: int = 1, iters: int = 3, fma_peak: float | None = None) -> dict:
+    import torch
+
+    from . import cuda_call_jit, families
+    from . import workloads as W
+
+    cfg = {k: v for k, v in W.VDP_CONFIG.items() if k not in ("n", "seed")}
+    call = cuda_call_jit(families.vdp_bs32(**cfg), grid=(n,),
+                         out_shape=(_shaped((n, 2)), _shaped((n,), np.int32), _shaped((n,), np.int32)),
+                         math_mode=math_mode)
+    dev = [torch.from_numpy(a).cuda() for a in W.van_der_pol_ensemble(n)]
+    out = call(*dev)
+    ms = _time(lambda: call(*dev), warmup, iters)
+    accepted, rejected = out[1].double(), out[2].double()
+    attempts = float((accepted + rejected).sum())
+    res = {"workload": "adaptive BS3(2) Van der Pol", "trajectories": n, "math_mode": str(math_mode), "ms": ms,
+           "attempts": attempts, "attempts_per_s": attempts / (ms * 1e-3),
+           "mean_attempts": attempts / n, "max_attempts": float((accepted + rejected).max()),
+           "mean_rejected": float(rejected.mean()), "trajectories_per_s": n / (ms * 1e-3)}
+    if fma_peak:
+        res["frac_of_fp32_peak"] = res["attempts_per_s"] * VDP_FLOPS_PER_ATTEMPT / fma_peak
+    return res
+
+
+def bench_gbm(n: int, math_mode="fast", warmup: int = 1, iters: int = 3, int_peak: float | None = None) -> dict:
+    import torch
+
+    from . import cuda_call_jit, families
+    from . import workloads as W
+
+    cfg = {k: v for k, v in W.GBM_CONFIG.items() if k not in ("n", "seed")}
+    call = cuda_call_jit(families.gbm_threefry(output="terminal", **cfg), grid=(n,),
+                         out_shape=(_shaped((n,)), _shaped((2,), np.float64)), math_mode=math_mode)
+    key = torch.from_numpy(W.gbm_key(0)).cuda()
+    out, sums = call(key)
+    ms = _time(lambda: call(key), warmup, iters)
+    s1, s2 = (float(v) for v in sums.cpu())
+    disc = float(np.exp(-cfg["r"] * cfg["t"]))
+    mean = s1 / n
+    stderr = disc * float(np.sqrt(max(s2 / n - mean * mean, 0.0) / n))
+    path_steps = float(n) * cfg["steps"]
+    res = {"workload": "GBM Monte Carlo, Threefry in-kernel", "paths": n, "steps": cfg["steps"],
+           "math_mode": str(math_mode), "ms": ms, "path_steps_per_s": path_steps / (ms * 1e-3),
+           "hashes_per_s": 4 * path_steps / (ms * 1e-3), "price": disc * mean, "stderr": stderr}
+    from math import erf, exp, log, sqrt
+
+    d1 = (log(cfg["s0"] / cfg["strike"]) + (cfg["r"] + cfg["sigma"] ** 2 / 2) * cfg["t"]) / (cfg["sigma"] * sqrt(cfg["t"]))
+    d2 = d1 - cfg["sigma"] * sqrt(cfg["t"])
+    cdf = lambda x: 0.5 * (1.0 + erf(x / sqrt(2.0)))  # noqa: E731
+    exact = cfg["s0"] * cdf(d1) - cfg["strike"] * exp(-cfg["r"] * cfg["t"]) * cdf(d2)
+    res["black_scholes"] = exact
+    res["sigmas_from_black_scholes"] = abs(res["price"] - exact) / stderr if stderr else None
+    if int_peak:
+        res["frac_of_int32_peak"] = res["path_steps_per_s"] * GBM_INT_OPS_PER_PATH_STEP / int_peak
+    return res
+
+
+def bench_gray_scott(size: int, steps: int, math_mode="fast", warmup: int = 1, iters: int = 3) -> dict:
+    import torch
+
+    from . import cuda_call_jit, families
+    from . import workloads as W
+
+    cfg = {k: v for k, v in W.GRAY_SCOTT_CONFIG.items() if k not in ("steps", "size", "seed")}
+    call = cuda_call_jit(families.gray_scott(steps=steps, **cfg), grid=(size, size),
+                         out_shape=(_shaped((size, size)), _shaped((size, size))), math_mode=math_mode)
+    u = torch.rand((size, size), device="cuda") * 0.5 + 0.5
+    v = torch.rand((size, size), device="cuda") * 0.25
+    ms = _time(lambda: call(u, v), warmup, iters)
+    cell_steps = float(size) * size * steps
+    peak, peak_note = _hbm_peak_gbs()
+    gbs = cell_steps * GS_BYTES_PER_CELL_STEP / (ms * 1e-3) / 1e9
+    return {"workload": "Gray-Scott periodic 5-point stencil", "size": size, "steps_per_call": steps,
+            "math_mode": str(math_mode), "ms": ms, "ms_per_step": ms / steps,
+            "cell_steps_per_s": cell_steps / (ms * 1e-3), "algorithmic_gbs": gbs, "hbm_peak_gbs": peak,
+            "frac_of_hbm_peak": gbs / peak, "peak_note": peak_note, "frac_of_8tbs_nominal": gbs / 8000.0}
+
+
+def bench_kepler(n: int, steps: int, warmup: int = 1, iters: int = 2, fma_peak: float | None = None) -> dict:
+    import torch
+
+    from . import cuda_call_jit, families
+    from . import workloads as W
+
+    call = cuda_call_jit(families.kepler_rk4_df32(dt=W.KEPLER_CONFIG["dt"], gm=1.0, steps=steps), grid=(n,),
+                         out_shape=tuple(_shaped((n,)) for _ in range(8)), math_mode="safe")
+    _, pairs = W.kepler_ensemble(n)
+    dev = [torch.from_numpy(a).cuda() for a in pairs]
+    ms = _time(lambda: call(*dev), warmup, iters)
+    ts = float(n) * steps
+    res = {"workload": "df32 RK4 Kepler orbits", "trajectories": n, "steps_per_call": steps, "ms": ms,
+           "trajectory_steps_per_s": ts / (ms * 1e-3), "flops_per_trajectory_step": DF32_KEPLER_FLOPS}
+    if fma_peak:
+        res["frac_of_fp32_peak"] = res["trajectory_steps_per_s"] * DF32_KEPLER_FLOPS / fma_peak
+    return res
+
+
+def bench_lv_df32(n: int, steps: int, warmup: int = 1, iters: int = 3, fma_peak: float | None = None) -> dict:
+    import torch
+
+    from . import cuda_call_jit, families
+    from . import workloads as W
+
+    call = cuda_call_jit(families.lv_rk4_df32(0.01, steps), grid=(n,), out_shape=(_shaped((n,)), _shaped((n,))),
+                         math_mode="safe")
+    dev = [torch.from_numpy(a).cuda() for a in W.lotka_volterra_ensemble(n)]
+    ms = _time(lambda: call(*dev), warmup, iters)
+    ts = float(n) * steps
+    res = {"workload": "df32 RK4 Lotka-Volterra", "trajectories": n, "steps_per_call": steps, "ms": ms,
+           "trajectory_steps_per_s": ts / (ms * 1e-3), "flops_per_trajectory_step": DF32_LV_FLOPS}
+    if fma_peak:
+        res["frac_of_fp32_peak"] = res["trajectory_steps_per_s"] * DF32_LV_FLOPS / fma_peak
+    return res
+
+
+def quick_summary() -> dict:
+    """Each family once, at a reduced size that finishes in a few seconds."""
+    from . import _native
+
+    fma_peak = _native.measure_fp32_fma_peak()
+    int_peak = _native.measure_int32_alu_peak()
+    out = {"fp32_fma_peak_tflops": fma_peak / 1e12, "int32_alu_peak_tops": int_peak / 1e12}
+    out["vdp_bs32"] = bench_vdp(1 << 18, "relaxed", fma_peak=fma_peak)
+    out["vdp_bs32_safe"] = bench_vdp(1 << 18, "safe", fma_peak=fma_peak)
+    out["gbm"] = bench_gbm(1 << 22, "fast", int_peak=int_peak)
+    out["gray_scott"] = bench_gray_scott(8192, 40, "fast")
+    out["kepler_df32"] = bench_kepler(1 << 20, 100, fma_peak=fma_peak)
+    out["lv_df32"] = bench_lv_df32(1 << 20, 100, fma_peak=fma_peak)
+    return out
+
+
+# ----------------------------------------------------------------------------- as the main workload
+def run(args, rank: int, local_rank: int, world: int, barrier, max_over_ranks) -> None:
+    import torch
+
+    from . import _native, sharded
+    from . import workloads as W
+
+    fma_peak = _native.measure_fp32_fma_peak()
+    int_peak = _native.measure_int32_alu_peak()
+    name = args.workload
+    steps, warmup = args.steps, max(args.warmup, 3)
+    line = {"n_gpus": world, "steps": steps, "warmup": warmup, "higher_is_better": True, "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "cpu_baseline": None, "e2e": None, "gpu_launches": None}
+    if name == "gbm":
+        n_local = args.n or (1 << 24)
+        n_total = n_local * world
+        cfg = {k: v for k, v in W.GBM_CONFIG.items() if k not in ("n", "seed")}
+        key = W.gbm_key(0)
+        for _ in range(warmup):
+            res = sharded.gbm_monte_carlo(key, n_total, cfg, math_mode=args.math_mode)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            res = sharded.gbm_monte_carlo(key, n_total, cfg, math_mode=args.math_mode)
+        e1.record()
+        barrier()
+        ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+        value = float(n_total) * cfg["steps"] / (ms * 1e-3)
+        line.update({"metric": "gbm_path_steps_per_s", "value": value, "unit": "path-steps/s", "ms_per_step": ms,
+                     "scaling": "weak", "dtype": "u32+f32", "gpu_launches": 2 * steps,
+                     "config": {"workload": "gbm_threefry_monte_carlo", "paths_per_gpu": n_local, "steps": cfg["steps"],
+                                "math_mode": args.math_mode, "collective": "one all_reduce of 2 float64 per step",
+                                "price": res.price, "stderr": res.stderr,
+                                "l2": "256 MB of per-path output per 2^26 paths; compute-bound"},
+                     "roofline": {"bound": "int32_alu", "achieved": value / world * GBM_INT_OPS_PER_PATH_STEP / 1e12,
+                                  "peak": int_peak / 1e12, "unit": "Tops/s",
+                                  "frac": value / world * GBM_INT_OPS_PER_PATH_STEP / int_peak, "traffic": None,
+                                  "peak_source": "add/xor/funnel-shift chain microbenchmark measured in this run"}})
+    elif name == "gray_scott":
+        size = args.n or 8192
+        rows_total = size * world if world > 1 else size
+        halo = 4
+        lo, hi = sharded.partition(rows_total, world, rank)
+        u = torch.rand((hi - lo, size), device="cuda") * 0.5 + 0.5
+        v = torch.rand((hi - lo, size), device="cuda") * 0.25
+        cfg = {k: v_ for k, v_ in W.GRAY_SCOTT_CONFIG.items() if k not in ("steps", "size", "seed")}
+        slab = sharded.GrayScottSlab(u, v, rows_total, halo=halo, constants=cfg, math_mode=args.math_mode)
+        per_step = 40
+        for _ in range(warmup):
+            slab.advance(per_step)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            slab.advance(per_step)
+        e1.record()
+        barrier()
+        ms = max_over_ranks(e0.elapsed_time(e1)) / steps
+        cell_steps = float(rows_total) * size * per_step
+        value = cell_steps / (ms * 1e-3)
+        peak, note = _hbm_peak_gbs()
+        gbs = value / world * GS_BYTES_PER_CELL_STEP / 1e9
+        line.update({"metric": "gray_scott_cell_steps_per_s", "value": value, "unit": "cell-steps/s", "ms_per_step": ms,
+                     "scaling": "weak", "gpu_launches": steps * per_step,
+                     "config": {"workload": "gray_scott_periodic", "rows": rows_total, "cols": size,
+                                "stencil_steps_per_bench_step": per_step, "halo": halo, "math_mode": args.math_mode,
+                                "parallelism": f"row slabs x{world}, halo exchange every {halo} steps",
+                                "l2": "fields are 268 MB each at 8192^2, larger than the 126 MB L2"},
+                     "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                                  "traffic": None, "peak_source": note}})
+    elif name == "vdp_bs32":
+        n = args.n or (1 << 20)
+        r = bench_vdp(n, args.math_mode if args.math_mode != "fast" else "relaxed", warmup=warmup, iters=steps, fma_peak=fma_peak)
+        ms = max_over_ranks(r["ms"])
+        value = r["attempts"] * world / (ms * 1e-3)
+        line.update({"metric": "bs32_attempted_steps_per_s", "value": value, "unit": "attempted steps/s",
+                     "ms_per_step": ms, "scaling": "weak", "gpu_launches": steps, "config": {"workload": "vdp_bs32", **r},
+                     "roofline": {"bound": "fp32_fma", "achieved": r["attempts_per_s"] * VDP_FLOPS_PER_ATTEMPT / 1e12,
+                                  "peak": fma_peak / 1e12, "unit": "TFLOP/s", "frac": r.get("frac_of_fp32_peak"),
+                                  "traffic": None}})
+    elif name == "kepler_df32":
+        n = args.n or (1 << 20)
+        r = bench_kepler(n, 1000, warmup=1, iters=steps, fma_peak=fma_peak)
+        ms = max_over_ranks(r["ms"])
+        value = float(n) * world * 1000 / (ms * 1e-3)
+        line.update({"metric": "df32_trajectory_steps_per_s", "value": value, "unit": "trajectory-steps/s",
+                     "ms_per_step": ms, "scaling": "weak", "gpu_launches": steps, "config": {"workload": "kepler_df32", **r},
+                     "roofline": {"bound": "fp32_fma", "achieved": r["trajectory_steps_per_s"] * DF32_KEPLER_FLOPS / 1e12,
+                                  "peak": fma_peak / 1e12, "unit": "TFLOP/s", "frac": r.get("frac_of_fp32_peak"),
+                                  "traffic": None}})
+    else:
+        raise SystemExit(f"unknown workload {name!r}")
+    if rank == 0:
+        print(json.dumps(line), flush=True)

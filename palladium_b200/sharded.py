@@ -1,0 +1,237 @@
+"""Multi-GPU execution: one process per GPU, `torch.distributed` for the plumbing.
+
+The reference has no multi-device code.  The three ways its kernels shard:
+
+* ODE ensembles (RK4, adaptive, df32): trajectories are independent, so rank r
+  integrates the contiguous slab `partition(n, world, r)`; no collective.
+* GBM Monte Carlo: paths are independent and the RNG stream of a path is keyed
+  by its *global* index (`path_offset`), so results do not depend on the number
+  of ranks; the per-rank float64 sums (payoff, payoff^2) are combined with ONE
+  all-reduce (NCCL over NVLink on GPUs).
+* Gray-Scott: row slabs on a periodic ring of ranks.  Each rank keeps `halo`
+  ghost rows above and below its owned rows; one exchange fills them from the
+  neighbours' boundary rows (point-to-point sends; the remote rows land in the
+  receiver's own memory before any kernel reads them), after which `halo` steps
+  run without communication (step s updates rows [s, rows + 2*halo - s), the
+  redundant ghost-row work replaces an exchange per step).  Per-cell arithmetic
+  is unchanged, so the result equals the single-grid result bit for bit.
+
+The step / path functions are injectable so the host logic (partitioning,
+exchange pattern, reduction) can be exercised by CPU ranks over gloo; the
+defaults run the CUDA kernels.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from collections.abc import Callable
+
+import numpy as np
+
+__all__ = ["partition", "GbmResult", "gbm_monte_carlo", "GrayScottSlab"]
+
+
+def partition(n: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous slab [lo, hi) of n units for `rank`; sizes differ by at most 1."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} is not in a world of {world}")
+    base, extra = divmod(int(n), world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def _dist():
+    import torch.distributed as dist
+
+    return dist
+
+
+def _world(group=None) -> tuple[int, int]:
+    dist = _dist()
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+# ----------------------------------------------------------------------------- Monte Carlo
+@dataclasses.dataclass
+class GbmResult:
+    price: float          # discounted mean payoff over ALL ranks' paths
+    stderr: float         # its standard error
+    n_total: int
+    local_lo: int
+    local_hi: int
+    local_output: object  # this rank's per-path output (device tensor or array)
+    sums: tuple[float, float]  # global (sum payoff, sum payoff^2)
+
+
+def _cuda_gbm_paths(key, lo: int, n_local: int, constants: dict, math_mode, output: str):
+    """Default path function: the CUDA kernel on this rank's GPU.  Returns
+    (per-path output tensor, float64 tensor [sum payoff, sum payoff^2])."""
+    import torch
+
+    from . import cuda_call_jit, families, pl
+
+    fam = families.gbm_threefry(output=output, path_offset=lo, **constants)
+    call = cuda_call_jit(fam, grid=(n_local,),
+                         out_shape=(pl.ShapeDtypeStruct((n_local,), np.float32), pl.ShapeDtypeStruct((2,), np.float64)),
+                         math_mode=math_mode)
+    key_dev = torch.from_numpy(np.asarray(key, np.uint32).copy()).cuda()
+    out, sums = call(key_dev)
+    return out, sums
+
+
+def gbm_monte_carlo(key, n_total: int, constants: dict, *, math_mode="fast", output: str = "terminal", group=None,
+                    path_fn: Callable | None = None) -> GbmResult:
+    """Price a European call over `n_total` GBM paths spread across the ranks of
+    `group` (examples/03_sde_montecarlo.py:137-146 computes the same price from
+    one device's payoffs).  `constants`: s0, strike, r, sigma, t, steps."""
+    import torch
+
+    dist = _dist()
+    rank, world = _world(group)
+    lo, hi = partition(n_total, world, rank)
+    fn = path_fn or _cuda_gbm_paths
+    out, sums = fn(key, lo, hi - lo, constants, math_mode, output)
+    sums_t = sums if isinstance(sums, torch.Tensor) else torch.as_tensor(np.asarray(sums, np.float64))
+    sums_t = sums_t.to(torch.float64).clone()
+    if world > 1:
+        dist.all_reduce(sums_t, op=dist.ReduceOp.SUM, group=group)
+    s1, s2 = (float(v) for v in sums_t.cpu())
+    disc = float(np.exp(-constants["r"] * constants["t"]))
+    mean = s1 / n_total
+    var = max(s2 / n_total - mean * mean, 0.0) * n_total / max(n_total - 1, 1)
+    return GbmResult(price=disc * mean, stderr=disc * float(np.sqrt(var / n_total)), n_total=n_total, local_lo=lo,
+                     local_hi=hi, local_output=out, sums=(s1, s2))
+
+
+# ----------------------------------------------------------------------------- stencil
+_SLAB_CALLS: dict = {}
+
+
+def _cuda_slab_step(u, v, steps: int, halo: int, rows: int, cols: int, constants: dict, math_mode):
+    """Default step function: `steps` (<= halo) stencil steps on a device slab."""
+    from . import cuda_call_jit, families, pl
+
+    key = (steps, halo, rows, cols, tuple(sorted(constants.items())), str(math_mode))
+    call = _SLAB_CALLS.get(key)
+    if call is None:
+        shape = (rows + 2 * halo, cols)
+        fam = families.gray_scott(steps=steps, halo=halo, **constants)
+        call = cuda_call_jit(fam, grid=(rows, cols),
+                             out_shape=(pl.ShapeDtypeStruct(shape, np.float32), pl.ShapeDtypeStruct(shape, np.float32)),
+                             math_mode=math_mode)
+        _SLAB_CALLS[key] = call
+    return call(u, v)
+
+
+class GrayScottSlab:
+    """One rank's row slab of a periodic (rows_total x cols) Gray-Scott grid.
+
+    Parameters
+    ----------
+    u, v : this rank's owned rows, shape (hi - lo, cols), as torch tensors on the
+        rank's device (CUDA for the default step function).
+    rows_total : global row count; this rank owns rows `partition(rows_total, world, rank)`.
+    halo : ghost rows per side = steps advanced per exchange.
+    """
+
+    def __init__(self, u, v, rows_total: int, *, halo: int = 4, constants: dict | None = None, math_mode="fast",
+                 group=None, step_fn: Callable | None = None):
+        import torch
+
+        self.group = group
+        self.rank, self.world = _world(group)
+        self.lo, self.hi = partition(rows_total, self.world, self.rank)
+        self.rows = self.hi - self.lo
+        self.cols = int(u.shape[1])
+        if tuple(u.shape) != (self.rows, self.cols) or tuple(v.shape) != (self.rows, self.cols):
+            raise ValueError(f"rank {self.rank} owns rows [{self.lo}, {self.hi}): expected fields of shape "
+                             f"{(self.rows, self.cols)}, got {tuple(u.shape)} and {tuple(v.shape)}")
+        if halo < 1:
+            raise ValueError("halo must be at least 1")
+        if self.rows < halo:
+            raise ValueError(f"a slab of {self.rows} rows cannot serve {halo} ghost rows to its neighbours")
+        self.halo = halo
+        self.constants = dict(constants or {})
+        self.math_mode = math_mode
+        self.step_fn = step_fn or _cuda_slab_step
+        shape = (self.rows + 2 * halo, self.cols)
+        self.u = torch.empty(shape, dtype=u.dtype, device=u.device)
+        self.v = torch.empty(shape, dtype=v.dtype, device=v.device)
+        self.u[halo:halo + self.rows] = u
+        self.v[halo:halo + self.rows] = v
+        self.up = (self.rank - 1) % self.world    # owns the rows above ours
+        self.down = (self.rank + 1) % self.world  # owns the rows below ours
+        self.exchanges = 0
+
+    # -- communication ----------------------------------------------------------------
+    def exchange(self) -> None:
+        """Fill the ghost rows: our first `halo` owned rows go to the upper
+        neighbour's bottom ghost rows, our last `halo` owned rows to the lower
+        neighbour's top ghost rows (periodic ring)."""
+        h, r = self.halo, self.rows
+        self.exchanges += 1
+        if self.world == 1:
+            for f in (self.u, self.v):
+                f[:h] = f[r:r + h]          # rows above row 0 are the last rows of the grid
+                f[h + r:] = f[h:2 * h]      # rows below the last row are the first rows
+            return
+        if self.world == 2:
+            # Both neighbours are the same rank: order the transfers explicitly so
+            # the two messages per field cannot be matched crosswise.
+            self._exchange_pairwise()
+            return
+        dist = _dist()
+        ops, keep = [], []
+        for f in (self.u, self.v):
+            top_send = f[h:2 * h].contiguous()
+            bot_send = f[r:r + h].contiguous()
+            keep += [top_send, bot_send]
+            ops += [dist.P2POp(dist.isend, top_send, self._global(self.up), group=self.group),
+                    dist.P2POp(dist.isend, bot_send, self._global(self.down), group=self.group),
+                    dist.P2POp(dist.irecv, f[:h], self._global(self.up), group=self.group),
+                    dist.P2POp(dist.irecv, f[h + r:], self._global(self.down), group=self.group)]
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+
+    def _exchange_pairwise(self) -> None:
+        dist = _dist()
+        h, r = self.halo, self.rows
+        other = self._global(self.up)
+        for f in (self.u, self.v):
+            top_send = f[h:2 * h].contiguous()
+            bot_send = f[r:r + h].contiguous()
+            top_recv = f[:h]
+            bot_recv = f[h + r:]
+            # message 1: my top rows -> the other's bottom ghosts; message 2: my bottom rows -> its top ghosts
+            first = [dist.P2POp(dist.isend, top_send, other, group=self.group),
+                     dist.P2POp(dist.irecv, bot_recv, other, group=self.group)]
+            for req in dist.batch_isend_irecv(first):
+                req.wait()
+            second = [dist.P2POp(dist.isend, bot_send, other, group=self.group),
+                      dist.P2POp(dist.irecv, top_recv, other, group=self.group)]
+            for req in dist.batch_isend_irecv(second):
+                req.wait()
+
+    def _global(self, group_rank: int) -> int:
+        dist = _dist()
+        if self.group is None:
+            return group_rank
+        return dist.get_global_rank(self.group, group_rank)
+
+    # -- stepping ---------------------------------------------------------------------
+    def advance(self, steps: int) -> None:
+        """Advance the whole grid by `steps` steps: ceil(steps / halo) exchanges."""
+        done = 0
+        while done < steps:
+            k = min(self.halo, steps - done)
+            self.exchange()
+            self.u, self.v = self.step_fn(self.u, self.v, k, self.halo, self.rows, self.cols, self.constants,
+                                          self.math_mode)
+            done += k
+
+    def owned(self):
+        """This rank's owned rows of u and v (views)."""
+        h = self.halo
+        return self.u[h:h + self.rows], self.v[h:h + self.rows]
