@@ -94,6 +94,31 @@ def gray_scott(u, v, *, steps: int, du=0.16, dv=0.08, f=0.035, k=0.065, dt=1.0):
     return u, v
 
 
+def gray_scott_slab(u, v, *, steps: int, halo: int, du=0.16, dv=0.08, f=0.035, k=0.065, dt=1.0):
+    """The same stencil on a row slab with `halo` ghost rows above and below:
+    periodic in columns only; step s (1-based) updates rows [s, rows_alloc - s)
+    and leaves the others as they were."""
+    u, v = np.asarray(u, F32).copy(), np.asarray(v, F32).copy()
+    if steps > halo:
+        raise ValueError("a slab can advance at most `halo` steps between exchanges")
+    DU, DV, F, FK, DT = F32(du), F32(dv), F32(f), F32(f + k), F32(dt)
+    four, one = F32(4.0), F32(1.0)
+    rows, cols = u.shape
+    jp = np.r_[1:cols, 0]
+    jm = np.r_[cols - 1, 0:cols - 1]
+    for s in range(1, steps + 1):
+        lo, hi = s, rows - s
+        uc, vc = u[lo:hi], v[lo:hi]
+        lap_u = u[lo + 1:hi + 1] + u[lo - 1:hi - 1] + uc[:, jp] + uc[:, jm] - four * uc
+        lap_v = v[lo + 1:hi + 1] + v[lo - 1:hi - 1] + vc[:, jp] + vc[:, jm] - four * vc
+        uvv = uc * vc * vc
+        nu = uc + DT * (DU * lap_u - uvv + F * (one - uc))
+        nv = vc + DT * (DV * lap_v + uvv - FK * vc)
+        u, v = u.copy(), v.copy()
+        u[lo:hi], v[lo:hi] = nu, nv
+    return u, v
+
+
 def gbm(key, n: int, *, s0, strike, r, sigma, t, steps: int, path_offset: int = 0):
     """examples/03_sde_montecarlo.py:97-119 with NumPy's float32 log/cos/exp,
     which are not the C library's: agreement with oracle.c is to rounding

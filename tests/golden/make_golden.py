@@ -1,0 +1,80 @@
+"""Generates the known-answer fixtures in this directory from the CPU oracle.
+
+    python tests/golden/make_golden.py
+
+Each .npz holds the seeded inputs and the oracle's outputs for one kernel
+family at a size the oracle finishes in well under a second.  The RK4 fixture
+additionally stores the output of the reference's own emitted kernel
+(tests/golden/rk4_lotka_volterra.metal in the reference, compiled for the CPU
+by oracle/build.py), which needs the reference checkout and is therefore
+produced here, once, rather than on the GPU box.  RNG vectors are the oracle's
+restatement of src/palladium/emit/rules.py:121-201; they are NOT vectors
+published for Threefry or produced by JAX (not installed), so they guard
+against drift, not against a shared misreading of the specification.
+"""
+
+import sys
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE.parent.parent))
+
+import oracle  # noqa: E402
+from palladium_b200 import workloads as W  # noqa: E402
+
+
+def main():
+    # ---- RK4 Lotka-Volterra: reference distributions and benchmark distributions
+    rng = np.random.default_rng(17)
+    n = 512
+    ref_args = [rng.uniform(lo, hi, n).astype(np.float32)
+                for lo, hi in ((0.8, 1.2), (0.8, 1.2), (0.9, 1.3), (0.3, 0.5), (0.08, 0.12), (0.3, 0.5))]
+    gx, gy = oracle.lv_rk4_reference_golden(*ref_args)   # the reference's emitted kernel, 500 steps
+    ox, oy = oracle.lv_rk4(*ref_args, dt=0.01, steps=500)
+    assert np.array_equal(gx, ox) and np.array_equal(gy, oy)
+    bench_args = W.lotka_volterra_ensemble(1000, seed=17)
+    bx, by = oracle.lv_rk4(*bench_args, dt=0.01, steps=1000)
+    np.savez_compressed(HERE / "lv_rk4.npz", ref_inputs=np.stack(ref_args), ref_golden_x=gx, ref_golden_y=gy,
+                        bench_inputs=np.stack(bench_args), bench_x=bx, bench_y=by)
+
+    # ---- Threefry
+    key = np.array([0x12345678, 0x9ABCDEF0], np.uint32)
+    data = np.array([0, 1, 17, 0xFFFFFFFF, 123456789], np.uint32)
+    np.savez_compressed(HERE / "threefry.npz", key=key, bits=oracle.random_bits(key, 64),
+                        uniform=oracle.uniform(key, 64), data=data, fold_in=oracle.fold_in(key, data),
+                        fold_uniform=oracle.fold_uniform(key, 8, 4),
+                        block=oracle.threefry2x32(key, np.array([7, 9], np.uint32)))
+
+    # ---- adaptive BS3(2): benchmark tolerances, both pow flavours
+    x0, v0, mu = W.van_der_pol_ensemble(64, seed=3)
+    cfg = dict(t1=20.0, rtol=1e-6, atol=1e-8, dt0=1e-3, max_steps=100_000)
+    pd_out = oracle.vdp_bs32(x0, v0, mu, pow="pd", **cfg)
+    libm_out = oracle.vdp_bs32(x0, v0, mu, pow="libm", **cfg)
+    np.savez_compressed(HERE / "vdp_bs32.npz", x0=x0, v0=v0, mu=mu, pd=np.stack(pd_out), libm=np.stack(libm_out))
+
+    # ---- GBM
+    gkey = W.gbm_key(0)
+    cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=252)
+    terminal, payoff = oracle.gbm(gkey, 2048, **cfg)
+    np.savez_compressed(HERE / "gbm.npz", key=gkey, terminal=terminal, payoff=payoff)
+
+    # ---- Gray-Scott
+    u0, v0g = W.gray_scott_initial_state(64, seed=11, patches=4, patch=16)
+    u, v = oracle.gray_scott(u0, v0g, steps=100)
+    np.savez_compressed(HERE / "gray_scott.npz", u0=u0, v0=v0g, u=u, v=v)
+
+    # ---- df32
+    lv_args = W.lotka_volterra_ensemble(256, seed=17)
+    dx, dy = oracle.lv_rk4_df32(*lv_args, dt=0.01, steps=500)
+    state64, pairs = W.kepler_ensemble(256, seed=5)
+    kout = oracle.kepler_rk4_df32(pairs, dt=1e-3, steps=1000)
+    truth = oracle.kepler_rk4_f64(state64, dt=1e-3, steps=1000)
+    np.savez_compressed(HERE / "df32.npz", lv_inputs=np.stack(lv_args), lv_x=dx, lv_y=dy, kepler_pairs=np.stack(pairs),
+                        kepler_out=np.stack(kout), kepler_truth=truth)
+    print("golden fixtures written to", HERE)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,200 @@
+"""The call objects on a real device: launch/wait, pin, concurrent use, the
+host-buffer C-ABI path and the device-tensor path.  Modelled on the reference's
+tests/test_dispatch_launch.py, tests/test_17_robustness.py and the parts of
+tests/test_11_ffi.py that do not need JAX."""
+
+import threading
+
+import numpy as np
+import pytest
+
+import oracle
+import palladium_b200 as pd
+from palladium_b200 import workloads as W
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+SAFE = pd.MathMode.SAFE
+
+
+def test_launch_then_wait_equals_call():
+    # tests/test_dispatch_launch.py:42-51
+    n = 1000
+    args = W.lotka_volterra_ensemble(n)
+    call = H.lv_solver(n, steps=100, math_mode=SAFE)
+    direct = call(*args)
+    pending = call.launch(*args)
+    assert isinstance(pending, pd.PendingResult)
+    waited = pending.wait()
+    np.testing.assert_array_equal(direct[0], waited[0])
+    np.testing.assert_array_equal(direct[1], waited[1])
+
+
+def test_second_launch_before_wait_does_not_corrupt_the_first():
+    # tests/test_dispatch_launch.py:74-87
+    n = 4096
+    a = W.lotka_volterra_ensemble(n, seed=1)
+    b = W.lotka_volterra_ensemble(n, seed=2)
+    call = H.lv_solver(n, steps=200, math_mode=SAFE)
+    first = call.launch(*a)
+    second = call.launch(*b)
+    got_b = second.wait()
+    got_a = first.wait()
+    np.testing.assert_array_equal(got_a[0], oracle.lv_rk4(*a, dt=0.01, steps=200)[0])
+    np.testing.assert_array_equal(got_b[0], oracle.lv_rk4(*b, dt=0.01, steps=200)[0])
+
+
+def test_stepping_loop_feeds_outputs_back():
+    # tests/test_dispatch_launch.py:54-72: outputs of one dispatch are the next one's inputs
+    size = 64
+    u, v = W.gray_scott_initial_state(size, patches=2, patch=8)
+    call = H.gs_solver(size, size, math_mode=SAFE)
+    cu, cv = u, v
+    for _ in range(5):
+        cu, cv = call.launch(cu, cv).wait()
+    want = oracle.gray_scott(u, v, steps=5)
+    np.testing.assert_array_equal(cu, want[0])
+    np.testing.assert_array_equal(cv, want[1])
+
+
+def test_pin_redispatches_on_resident_inputs():
+    n = 2000
+    args = [a.copy() for a in W.lotka_volterra_ensemble(n)]
+    call = H.lv_solver(n, steps=50, math_mode=SAFE)
+    pinned = call.pin(*args)
+    want = oracle.lv_rk4(*args, dt=0.01, steps=50)
+    args[0][:] = 0.0  # later mutation of the passed arrays is not observed
+    for _ in range(3):
+        got = pinned()
+        np.testing.assert_array_equal(got[0], want[0])
+        np.testing.assert_array_equal(got[1], want[1])
+
+
+def test_single_output_is_a_bare_array_and_outputs_are_fresh():
+    key = W.gbm_key(1)
+    call = H.gbm_solver(512, math_mode=SAFE, steps=16)
+    first = call(key)
+    second = call(key)
+    assert isinstance(first, np.ndarray) and first.shape == (512,)
+    assert first is not second and not np.shares_memory(first, second)
+    np.testing.assert_array_equal(first, second)
+
+
+def test_many_threads_share_one_bound_kernel():
+    # tests/test_17_robustness.py:52-78
+    n = 3000
+    call = H.lv_solver(n, steps=40, math_mode=SAFE)
+    inputs = [W.lotka_volterra_ensemble(n, seed=s) for s in range(8)]
+    wants = [oracle.lv_rk4(*a, dt=0.01, steps=40) for a in inputs]
+    results = [None] * 8
+    errors = []
+
+    def worker(i):
+        try:
+            results[i] = call(*inputs[i])
+        except Exception as exc:  # surfaced below
+            errors.append(exc)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(8)]
+    [t.start() for t in threads]
+    [t.join() for t in threads]
+    assert not errors
+    assert len(call.cache) == 1
+    for got, want in zip(results, wants):
+        np.testing.assert_array_equal(got[0], want[0])
+        np.testing.assert_array_equal(got[1], want[1])
+
+
+def test_host_buffer_path_matches_eager_and_oracle():
+    """cuda_call_jit on NumPy arrays goes through pd_dispatch_host, the call an
+    XLA:CPU FFI handler would make (tests/test_11_ffi.py:35-60: eager == interpret)."""
+    n = 5001
+    args = W.lotka_volterra_ensemble(n)
+    jit = H.lv_solver(n, steps=120, call=pd.cuda_call_jit, math_mode=SAFE)
+    got = jit(*args)
+    want = oracle.lv_rk4(*args, dt=0.01, steps=120)
+    np.testing.assert_array_equal(got[0], want[0])
+    np.testing.assert_array_equal(got[1], want[1])
+
+
+def test_host_buffer_path_from_many_threads():
+    n = 1024
+    jit = H.lv_solver(n, steps=30, call=pd.cuda_call_jit, math_mode=SAFE)
+    inputs = [W.lotka_volterra_ensemble(n, seed=s) for s in range(6)]
+    results = [None] * 6
+
+    def worker(i):
+        results[i] = jit(*inputs[i])
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(6)]
+    [t.start() for t in threads]
+    [t.join() for t in threads]
+    for a, got in zip(inputs, results):
+        np.testing.assert_array_equal(got[0], oracle.lv_rk4(*a, dt=0.01, steps=30)[0])
+
+
+def test_device_tensor_path_is_stream_ordered_and_composes_with_torch_ops():
+    import torch
+
+    n = 4096
+    args = W.lotka_volterra_ensemble(n)
+    jit = H.lv_solver(n, steps=60, call=pd.cuda_call_jit, math_mode=SAFE)
+    dev = [torch.from_numpy(a).cuda() for a in args]
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        scaled = dev[0] * 1.0                       # a torch op before ...
+        x, y = jit(scaled, *dev[1:])
+        total = (x * x + y * y).sum()               # ... and after, on the same stream, no sync in between
+    stream.synchronize()
+    want = oracle.lv_rk4(*args, dt=0.01, steps=60)
+    np.testing.assert_array_equal(x.cpu().numpy(), want[0])
+    np.testing.assert_allclose(float(total), float((want[0].astype(np.float64) ** 2 + want[1].astype(np.float64) ** 2).sum()), rtol=1e-5)
+
+
+def test_multi_output_and_math_mode_reach_the_kernel():
+    """Different math modes must select different compiled kernels
+    (tests/test_11_ffi.py:123-145 checks the same by a NaN probe): SAFE equals
+    the oracle bit for bit, FAST does not."""
+    n = 20_000
+    args = W.lotka_volterra_ensemble(n)
+    safe = H.lv_solver(n, steps=500, call=pd.cuda_call_jit, math_mode=SAFE)(*args)
+    fast = H.lv_solver(n, steps=500, call=pd.cuda_call_jit, math_mode=pd.MathMode.FAST)(*args)
+    want = oracle.lv_rk4(*args, dt=0.01, steps=500)
+    assert np.array_equal(safe[0], want[0])
+    assert not np.array_equal(fast[0], want[0])
+    np.testing.assert_allclose(fast[0], want[0], rtol=1e-4)
+
+
+def test_unaligned_host_and_device_buffers_take_the_scalar_path():
+    import torch
+
+    n = 1003
+    args = W.lotka_volterra_ensemble(n)
+    backing = [torch.empty(n + 1, dtype=torch.float32, device="cuda") for _ in range(6)]
+    views = [b[1:] for b in backing]  # 4-byte aligned only
+    for v, a in zip(views, args):
+        v.copy_(torch.from_numpy(a))
+    jit = H.lv_solver(n, steps=25, call=pd.cuda_call_jit, math_mode=SAFE)
+    x, y = jit(*[v.contiguous() if False else v for v in views])
+    want = oracle.lv_rk4(*args, dt=0.01, steps=25)
+    np.testing.assert_array_equal(x.cpu().numpy(), want[0])
+
+
+def test_explain_on_device_reports_registers_and_occupancy():
+    diag = H.lv_solver(1 << 20).explain(*[H.shaped(1 << 20)] * 6)
+    assert diag.regs > 0 and diag.blocks_per_sm > 0 and diag.smem_bytes >= 0
+
+
+def test_empty_ensemble():
+    call = H.lv_solver(0, steps=10, math_mode=SAFE)
+    x, y = call(*[np.zeros(0, np.float32)] * 6)
+    assert x.shape == (0,) and y.shape == (0,)
+
+
+def test_peak_measurements_are_plausible():
+    from palladium_b200 import _native
+
+    fma = _native.measure_fp32_fma_peak()
+    alu = _native.measure_int32_alu_peak()
+    assert 30e12 < fma < 90e12
+    assert 5e12 < alu < 60e12

@@ -1,0 +1,72 @@
+"""Two (or more) GPUs, one process each, NCCL: the Gray-Scott halo exchange and
+the Monte Carlo all-reduce with the CUDA kernels.  Skipped on a single GPU."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+
+import oracle
+from palladium_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+
+    from palladium_b200 import sharded
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        rows, cols, steps, halo = 256, 512, 18, 4
+        u0, v0 = W.gray_scott_initial_state(512, seed=11, patches=16, patch=32)
+        u0, v0 = u0[:rows].copy(), v0[:rows].copy()
+        lo, hi = sharded.partition(rows, world, rank)
+        slab = sharded.GrayScottSlab(torch.from_numpy(u0[lo:hi]).cuda(), torch.from_numpy(v0[lo:hi]).cuda(), rows,
+                                     halo=halo, constants=dict(oracle.GS_DEFAULTS), math_mode="safe")
+        slab.advance(steps)
+        u, v = slab.owned()
+        cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=64)
+        res = sharded.gbm_monte_carlo(W.gbm_key(0), 100_003, cfg, math_mode="safe")
+        torch.cuda.synchronize()
+        np.savez(os.path.join(out_dir, f"r{rank}.npz"), u=u.cpu().numpy(), v=v.cpu().numpy(), lo=lo, hi=hi,
+                 price=res.price, sums=np.array(res.sums), out=res.local_output.cpu().numpy(), plo=res.local_lo)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpus_halo_exchange_and_all_reduce(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    rows, steps = 256, 18
+    u0, v0 = W.gray_scott_initial_state(512, seed=11, patches=16, patch=32)
+    want_u, want_v = oracle.gray_scott(u0[:rows].copy(), v0[:rows].copy(), steps=steps)
+    cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=64)
+    terminal, payoff = oracle.gbm(W.gbm_key(0), 100_003, **cfg)
+    p64 = payoff.astype(np.float64)
+    outs = []
+    for rank in range(world):
+        part = np.load(tmp_path / f"r{rank}.npz")
+        lo, hi = int(part["lo"]), int(part["hi"])
+        np.testing.assert_array_equal(part["u"], want_u[lo:hi])
+        np.testing.assert_array_equal(part["v"], want_v[lo:hi])
+        np.testing.assert_allclose(part["sums"][0], p64.sum(), rtol=1e-5)
+        outs.append(part["out"])
+    np.testing.assert_allclose(np.concatenate(outs), terminal, rtol=1e-5)

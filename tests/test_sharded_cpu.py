@@ -1,0 +1,123 @@
+"""Multi-rank host logic on CPU ranks (gloo): partitioning, the Gray-Scott halo
+exchange pattern, and the Monte Carlo reduction.  The step / path functions are
+the oracle's, so what is tested is exactly the code that decides who owns what,
+what is sent where, and how partial results combine."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from oracle import oracle_np
+from palladium_b200 import sharded
+from palladium_b200 import workloads as W
+
+
+def test_partition_covers_everything_once():
+    for n in (0, 1, 7, 100, 100_000):
+        for world in (1, 2, 3, 8):
+            slabs = [sharded.partition(n, world, r) for r in range(world)]
+            assert slabs[0][0] == 0 and slabs[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(slabs, slabs[1:]))
+            sizes = [hi - lo for lo, hi in slabs]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        sharded.partition(10, 2, 2)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _np_slab_step(u, v, steps, halo, rows, cols, constants, math_mode):
+    nu, nv = oracle_np.gray_scott_slab(u.numpy(), v.numpy(), steps=steps, halo=halo, **constants)
+    return torch.from_numpy(nu), torch.from_numpy(nv)
+
+
+def _oracle_paths(key, lo, n_local, constants, math_mode, output):
+    terminal, payoff = oracle.gbm(key, n_local, path_offset=lo, **constants)
+    p64 = payoff.astype(np.float64)
+    return torch.from_numpy(terminal), np.array([p64.sum(), (p64 * p64).sum()])
+
+
+def _worker(rank, world, port, case, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        if case == "gray_scott":
+            rows, cols, steps, halo = 48, 20, 11, 3
+            u0, v0 = W.gray_scott_initial_state(rows, seed=11, patches=3, patch=8)
+            u0, v0 = u0[:, :cols].copy(), v0[:, :cols].copy()
+            lo, hi = sharded.partition(rows, world, rank)
+            slab = sharded.GrayScottSlab(torch.from_numpy(u0[lo:hi]), torch.from_numpy(v0[lo:hi]), rows, halo=halo,
+                                         constants=dict(oracle.GS_DEFAULTS), step_fn=_np_slab_step)
+            slab.advance(steps)
+            u, v = slab.owned()
+            np.savez(os.path.join(out_dir, f"gs_{rank}.npz"), u=u.numpy(), v=v.numpy(), lo=lo, hi=hi,
+                     exchanges=slab.exchanges)
+        elif case == "gbm":
+            cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=32)
+            res = sharded.gbm_monte_carlo(W.gbm_key(0), 1001, cfg, path_fn=_oracle_paths)
+            np.savez(os.path.join(out_dir, f"gbm_{rank}.npz"), price=res.price, stderr=res.stderr, lo=res.local_lo,
+                     hi=res.local_hi, out=res.local_output.numpy(), sums=np.array(res.sums))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world, case, tmp_path):
+    mp.spawn(_worker, args=(world, _free_port(), case, str(tmp_path)), nprocs=world, join=True)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_gray_scott_slabs_with_halo_exchange_equal_the_periodic_grid(world, tmp_path):
+    _run(world, "gray_scott", tmp_path)
+    rows, cols, steps = 48, 20, 11
+    u0, v0 = W.gray_scott_initial_state(rows, seed=11, patches=3, patch=8)
+    want_u, want_v = oracle.gray_scott(u0[:, :cols].copy(), v0[:, :cols].copy(), steps=steps)
+    for rank in range(world):
+        part = np.load(tmp_path / f"gs_{rank}.npz")
+        lo, hi = int(part["lo"]), int(part["hi"])
+        np.testing.assert_array_equal(part["u"], want_u[lo:hi])
+        np.testing.assert_array_equal(part["v"], want_v[lo:hi])
+        assert int(part["exchanges"]) == 4  # ceil(11 / 3)
+
+
+def test_gray_scott_single_rank_wraps_its_own_halo():
+    rows, cols, steps = 32, 16, 7
+    u0, v0 = W.gray_scott_initial_state(rows, patches=2, patch=8)
+    u0, v0 = u0[:, :cols].copy(), v0[:, :cols].copy()
+    slab = sharded.GrayScottSlab(torch.from_numpy(u0), torch.from_numpy(v0), rows, halo=4,
+                                 constants=dict(oracle.GS_DEFAULTS), step_fn=_np_slab_step)
+    slab.advance(steps)
+    want = oracle.gray_scott(u0, v0, steps=steps)
+    np.testing.assert_array_equal(slab.owned()[0].numpy(), want[0])
+    np.testing.assert_array_equal(slab.owned()[1].numpy(), want[1])
+
+
+def test_slab_argument_checks():
+    u = torch.zeros(8, 4)
+    with pytest.raises(ValueError, match="expected fields of shape"):
+        sharded.GrayScottSlab(u, u, 16, halo=2, step_fn=_np_slab_step)
+    with pytest.raises(ValueError, match="cannot serve"):
+        sharded.GrayScottSlab(u, u, 8, halo=9, step_fn=_np_slab_step)
+
+
+def test_gbm_all_reduce_matches_single_rank(tmp_path):
+    _run(2, "gbm", tmp_path)
+    cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=32)
+    single = sharded.gbm_monte_carlo(W.gbm_key(0), 1001, cfg, path_fn=_oracle_paths)
+    parts = [np.load(tmp_path / f"gbm_{r}.npz") for r in range(2)]
+    for part in parts:
+        np.testing.assert_allclose(part["sums"], single.sums, rtol=1e-13)
+        np.testing.assert_allclose(float(part["price"]), single.price, rtol=1e-13)
+    # the slabs are contiguous and the per-path results do not depend on the rank count
+    assert int(parts[0]["lo"]) == 0 and int(parts[0]["hi"]) == int(parts[1]["lo"]) and int(parts[1]["hi"]) == 1001
+    np.testing.assert_array_equal(np.concatenate([p["out"] for p in parts]), single.local_output.numpy())
