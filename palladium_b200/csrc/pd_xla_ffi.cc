@@ -1,0 +1,71 @@
+// pd_xla_ffi.cc -- XLA-FFI handler symbol `palladium_cuda_dispatch`.
+//
+// The counterpart of XLA_FFI_DEFINE_HANDLER_SYMBOL(palladium_dispatch, ...) in
+// the reference (native/ffi/palladium_ffi.cpp:197-209).  The attribute list is
+// the reference's with `msl_source` / `function_name` replaced by `family` and
+// the family's parameter block (`params`, the bytes of the pd_*_params struct);
+// grid, threadgroup and math_mode keep their names and meaning, and the buffers
+// still arrive as RemainingArgs / RemainingRets, so one handler serves every
+// family and any input / output count.
+//
+// Registered on the "cpu" platform, like the reference's handler
+// (src/palladium/ffi.py:78): XLA hands it host buffers and the call blocks until
+// the outputs are in place, which is exactly pd_dispatch_host.
+//
+// This file needs the XLA FFI headers (`jax.ffi.include_dir()`); it is not part
+// of the default build and is compiled by palladium_b200/xla_ffi.py only where
+// JAX is installed.
+#include <cstdint>
+#include <vector>
+
+#include "../../include/palladium_cuda.h"
+#include "xla/ffi/api/ffi.h"
+
+namespace ffi = xla::ffi;
+
+static ffi::Error PalladiumCudaDispatch(int64_t family, ffi::Span<const uint8_t> params, int64_t grid_x,
+                                        int64_t grid_y, int64_t grid_z, int64_t threadgroup_x,
+                                        int64_t threadgroup_y, int64_t threadgroup_z, int64_t math_mode,
+                                        ffi::RemainingArgs args, ffi::RemainingRets rets) {
+  std::vector<const void*> in;
+  std::vector<size_t> in_bytes;
+  std::vector<void*> out;
+  std::vector<size_t> out_bytes;
+  in.reserve(args.size());
+  out.reserve(rets.size());
+  for (size_t i = 0; i < args.size(); ++i) {
+    auto buf = args.get<ffi::AnyBuffer>(i);
+    if (!buf.has_value()) return buf.error();
+    in.push_back(buf->untyped_data());
+    in_bytes.push_back(buf->size_bytes());
+  }
+  for (size_t i = 0; i < rets.size(); ++i) {
+    auto buf = rets.get<ffi::AnyBuffer>(i);
+    if (!buf.has_value()) return buf.error();
+    out.push_back((*buf)->untyped_data());
+    out_bytes.push_back((*buf)->size_bytes());
+  }
+  const int64_t grid[3] = {grid_x, grid_y, grid_z};
+  const int64_t block[3] = {threadgroup_x, threadgroup_y, threadgroup_z};
+  char err[1024] = {0};
+  const int rc = pd_dispatch_host(static_cast<int>(family), params.begin(), params.size(), static_cast<int>(math_mode),
+                                  grid, block, static_cast<int>(in.size()), in.data(), in_bytes.data(),
+                                  static_cast<int>(out.size()), out.data(), out_bytes.data(), err, sizeof err);
+  if (rc == PD_ERR_INVALID_ARGUMENT) return ffi::Error::InvalidArgument(err);
+  if (rc != PD_OK) return ffi::Error::Internal(err);
+  return ffi::Error::Success();
+}
+
+XLA_FFI_DEFINE_HANDLER_SYMBOL(palladium_cuda_dispatch, PalladiumCudaDispatch,
+                              ffi::Ffi::Bind()
+                                  .Attr<int64_t>("family")
+                                  .Attr<ffi::Span<const uint8_t>>("params")
+                                  .Attr<int64_t>("grid_x")
+                                  .Attr<int64_t>("grid_y")
+                                  .Attr<int64_t>("grid_z")
+                                  .Attr<int64_t>("threadgroup_x")
+                                  .Attr<int64_t>("threadgroup_y")
+                                  .Attr<int64_t>("threadgroup_z")
+                                  .Attr<int64_t>("math_mode")
+                                  .RemainingArgs()
+                                  .RemainingRets());
