@@ -614,9 +614,12 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
 }
 
 // Per-thread staging state for pd_dispatch_host.
+const int kHostStreams = 3;
 struct HostStaging {
     int device = -1;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;                 // stream 0, also used for unchunked calls
+    cudaStream_t streams[kHostStreams] = {nullptr, nullptr, nullptr};
+    cudaEvent_t broadcast_done = nullptr;
     std::vector<ScratchSlot> slots;
     ~HostStaging() {
         // Device memory is reclaimed when the context goes away; freeing here
@@ -663,9 +666,16 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
     if (hs.device != dev.device) {
         hs.device = dev.device;
         hs.stream = nullptr;
+        for (int i = 0; i < kHostStreams; ++i) hs.streams[i] = nullptr;
+        hs.broadcast_done = nullptr;
         hs.slots.clear();
     }
-    if (!hs.stream) PD_CUDA_TRY(cudaStreamCreateWithFlags(&hs.stream, cudaStreamNonBlocking));
+    if (!hs.stream) {
+        for (int i = 0; i < kHostStreams; ++i)
+            PD_CUDA_TRY(cudaStreamCreateWithFlags(&hs.streams[i], cudaStreamNonBlocking));
+        hs.stream = hs.streams[0];
+        PD_CUDA_TRY(cudaEventCreateWithFlags(&hs.broadcast_done, cudaEventDisableTiming));
+    }
     const int total = n_in + n_out;
     if ((int)hs.slots.size() < total) hs.slots.resize(total);
     std::vector<const void*> d_in(n_in);
@@ -682,20 +692,106 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
         }
         if (i < n_in) d_in[i] = slot.ptr; else d_out[i - n_in] = slot.ptr;
     }
-    for (int i = 0; i < n_in; ++i) {
+    for (int i = 0; i < n_in; ++i)
         if (in_bytes[i] && !in[i]) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "input %d: NULL pointer", i);
-        if (in_bytes[i]) PD_CUDA_TRY(cudaMemcpyAsync(hs.slots[i].ptr, in[i], in_bytes[i], cudaMemcpyHostToDevice, hs.stream));
+    for (int i = 0; i < n_out; ++i)
+        if (out_bytes[i] && !out[i]) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output %d: NULL pointer", i);
+
+    // ---- chunked pipeline for the per-trajectory families ------------------------------
+    // Trajectories (paths) are independent, so a large call is cut into chunks
+    // that travel round-robin over three streams: while chunk c integrates, the
+    // inputs of chunk c+1 are uploading and the results of chunk c-1 are
+    // downloading.  A buffer whose size is not proportional to the trajectory
+    // count (the RNG key) is uploaded once and the chunk streams wait for it.
+    const bool per_item_family = family == PD_FAMILY_LV_RK4 || family == PD_FAMILY_VDP_BS32 ||
+                                 family == PD_FAMILY_LV_RK4_DF32 || family == PD_FAMILY_KEPLER_RK4_DF32 ||
+                                 (family == PD_FAMILY_GBM_THREEFRY && n_out == 1);
+    const int64_t n = grid ? grid[0] : 0;
+    const int64_t kMinChunked = (int64_t)1 << 18;
+    bool chunked = per_item_family && n >= kMinChunked && params && params_bytes <= 256;
+    std::vector<size_t> in_item(n_in, 0), out_item(n_out, 0);
+    if (chunked) {
+        for (int i = 0; i < n_in; ++i)
+            if (in_bytes[i] % (size_t)n == 0 && in_bytes[i] / (size_t)n >= 4) in_item[i] = in_bytes[i] / (size_t)n;
+        for (int i = 0; i < n_out; ++i) {
+            if (out_bytes[i] % (size_t)n == 0 && out_bytes[i] / (size_t)n >= 4) out_item[i] = out_bytes[i] / (size_t)n;
+            else chunked = false;
+        }
     }
+    if (chunked) {
+        int64_t chunk = ((n + 11) / 12 + 4095) / 4096 * 4096;  // ~12 chunks, 16 KiB-aligned slices
+        if (chunk < ((int64_t)1 << 16)) chunk = (int64_t)1 << 16;
+        bool any_broadcast = false;
+        for (int i = 0; i < n_in; ++i) {
+            if (in_item[i] == 0 && in_bytes[i]) {
+                PD_CUDA_TRY(cudaMemcpyAsync(hs.slots[i].ptr, in[i], in_bytes[i], cudaMemcpyHostToDevice, hs.streams[0]));
+                any_broadcast = true;
+            }
+        }
+        if (any_broadcast) {
+            PD_CUDA_TRY(cudaEventRecord(hs.broadcast_done, hs.streams[0]));
+            for (int sidx = 1; sidx < kHostStreams; ++sidx)
+                PD_CUDA_TRY(cudaStreamWaitEvent(hs.streams[sidx], hs.broadcast_done, 0));
+        }
+        unsigned char local_params[256];
+        memcpy(local_params, params, params_bytes);
+        int rc = PD_OK;
+        int c = 0;
+        std::vector<const void*> c_in(n_in);
+        std::vector<void*> c_out(n_out);
+        std::vector<size_t> c_in_bytes(n_in), c_out_bytes(n_out);
+        for (int64_t lo = 0; lo < n && rc == PD_OK; lo += chunk, ++c) {
+            const int64_t len = (n - lo < chunk) ? n - lo : chunk;
+            cudaStream_t st = hs.streams[c % kHostStreams];
+            for (int i = 0; i < n_in; ++i) {
+                if (in_item[i]) {
+                    const size_t off = (size_t)lo * in_item[i];
+                    c_in[i] = (const char*)hs.slots[i].ptr + off;
+                    c_in_bytes[i] = (size_t)len * in_item[i];
+                    PD_CUDA_TRY(cudaMemcpyAsync((char*)hs.slots[i].ptr + off, (const char*)in[i] + off, c_in_bytes[i],
+                                                cudaMemcpyHostToDevice, st));
+                } else {
+                    c_in[i] = hs.slots[i].ptr;
+                    c_in_bytes[i] = in_bytes[i];
+                }
+            }
+            for (int i = 0; i < n_out; ++i) {
+                c_out[i] = (char*)hs.slots[n_in + i].ptr + (size_t)lo * out_item[i];
+                c_out_bytes[i] = (size_t)len * out_item[i];
+            }
+            if (family == PD_FAMILY_GBM_THREEFRY) {
+                pd_gbm_params gp;
+                memcpy(&gp, params, sizeof(gp));
+                gp.path_offset += lo;
+                memcpy(local_params, &gp, sizeof(gp));
+            }
+            const int64_t c_grid[3] = {len, grid[1], grid[2]};
+            rc = launch_impl(family, local_params, params_bytes, math_mode, c_grid, block, n_in, c_in.data(),
+                             c_in_bytes.data(), n_out, c_out.data(), c_out_bytes.data(), nullptr, 0, st, err, err_cap);
+            if (rc) break;
+            for (int i = 0; i < n_out; ++i)
+                PD_CUDA_TRY(cudaMemcpyAsync((char*)out[i] + (size_t)lo * out_item[i], c_out[i], c_out_bytes[i],
+                                            cudaMemcpyDeviceToHost, st));
+        }
+        for (int sidx = 0; sidx < kHostStreams; ++sidx) {
+            cudaError_t e = cudaStreamSynchronize(hs.streams[sidx]);
+            if (e != cudaSuccess && rc == PD_OK)
+                rc = fail(PD_ERR_CUDA, err, err_cap, "cudaStreamSynchronize failed: %s", cudaGetErrorString(e));
+        }
+        return rc;
+    }
+
+    // ---- one upload, one launch sequence, one download --------------------------------
+    for (int i = 0; i < n_in; ++i)
+        if (in_bytes[i]) PD_CUDA_TRY(cudaMemcpyAsync(hs.slots[i].ptr, in[i], in_bytes[i], cudaMemcpyHostToDevice, hs.stream));
     int rc = launch_impl(family, params, params_bytes, math_mode, grid, block, n_in, d_in.data(), in_bytes, n_out,
                          d_out.data(), out_bytes, nullptr, 0, hs.stream, err, err_cap);
     if (rc) {
         cudaStreamSynchronize(hs.stream);
         return rc;
     }
-    for (int i = 0; i < n_out; ++i) {
-        if (out_bytes[i] && !out[i]) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output %d: NULL pointer", i);
+    for (int i = 0; i < n_out; ++i)
         if (out_bytes[i]) PD_CUDA_TRY(cudaMemcpyAsync(out[i], d_out[i], out_bytes[i], cudaMemcpyDeviceToHost, hs.stream));
-    }
     PD_CUDA_TRY(cudaStreamSynchronize(hs.stream));
     return PD_OK;
 }

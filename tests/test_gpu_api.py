@@ -198,3 +198,38 @@ def test_peak_measurements_are_plausible():
     alu = _native.measure_int32_alu_peak()
     assert 30e12 < fma < 90e12
     assert 5e12 < alu < 60e12
+
+
+# ------------------------------------------------------------------ chunked host pipeline
+def test_large_host_call_is_chunked_and_still_exact():
+    """Above 2^18 trajectories pd_dispatch_host pipelines upload / compute /
+    download in chunks; results must not depend on the chunking."""
+    n = (1 << 18) + 12_345
+    args = W.lotka_volterra_ensemble(n)
+    got = H.lv_solver(n, steps=20, call=pd.cuda_call_jit, math_mode=SAFE)(*args)
+    want = oracle.lv_rk4(*args, dt=0.01, steps=20)
+    np.testing.assert_array_equal(got[0], want[0])
+    np.testing.assert_array_equal(got[1], want[1])
+
+
+def test_chunked_gbm_keeps_global_path_indices():
+    import torch
+
+    n = (1 << 18) + 77
+    key = W.gbm_key(4)
+    host = H.gbm_solver(n, call=pd.cuda_call_jit, math_mode=SAFE, output="terminal", steps=8)(key)
+    dev = H.gbm_solver(n, call=pd.cuda_call_jit, math_mode=SAFE, output="terminal", steps=8)(torch.from_numpy(key).cuda())
+    np.testing.assert_array_equal(host, dev.cpu().numpy())
+    np.testing.assert_allclose(host[:4096], oracle.gbm(key, 4096, s0=100.0, strike=105.0, r=0.03, sigma=0.2, t=1.0, steps=8)[0], rtol=1e-5)
+
+
+def test_chunked_adaptive_counts_are_exact():
+    n = 1 << 18
+    x0, v0, mu = W.van_der_pol_ensemble(n)
+    cfg = dict(t1=0.5, rtol=1e-5, atol=1e-7, dt0=1e-2, max_steps=400)
+    state, accepted, rejected = H.vdp_solver(n, outputs=3, call=pd.cuda_call_jit, math_mode=SAFE, **cfg)(x0, v0, mu)
+    pick = np.r_[0:300, n // 2:n // 2 + 300, n - 300:n]
+    want = oracle.vdp_bs32(x0[pick], v0[pick], mu[pick], pow="pd", **cfg)
+    np.testing.assert_array_equal(state[pick, 0], want[1])
+    np.testing.assert_array_equal(accepted[pick], want[5].astype(np.int32))
+    np.testing.assert_array_equal(rejected[pick], want[4].astype(np.int32))
