@@ -275,7 +275,7 @@ def run(args, rank: int, local_rank: int, world: int, barrier, max_over_ranks) -
                                   "traffic": None, "peak_source": note}})
     elif name == "vdp_bs32":
         n = args.n or (1 << 20)
-        r = bench_vdp(n, args.math_mode if args.math_mode != "fast" else "relaxed", warmup=warmup, iters=steps, fma_peak=fma_peak)
+        r = bench_vdp(n, args.math_mode, warmup=warmup, iters=steps, fma_peak=fma_peak)
         ms = max_over_ranks(r["ms"])
         value = r["attempts"] * world / (ms * 1e-3)
         line.update({"metric": "bs32_attempted_steps_per_s", "value": value, "unit": "attempted steps/s",

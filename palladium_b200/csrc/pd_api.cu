@@ -232,9 +232,15 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 plan->grid[0] = (n + b - 1) / b;
             } else {
                 plan->kernel_name = "pd_vdp_refill_kernel";
+                // About 1024 resident threads per SM measured best: enough warps to
+                // hide the divide / pow latencies, and few enough threads that each one
+                // integrates many trajectories, which evens out the heavy-tailed work.
                 int per_sm = (int)knob("vdp_blocks_per_sm");
-                if (!per_sm) per_sm = dev.present ? occupancy_blocks(plan->kernel, b) : 0;
-                if (per_sm <= 0) per_sm = 2048 / b / 2;
+                if (!per_sm) {
+                    per_sm = 1024 / b > 0 ? 1024 / b : 1;
+                    const int occ = dev.present ? occupancy_blocks(plan->kernel, b) : 0;
+                    if (occ > 0 && per_sm > occ) per_sm = occ;
+                }
                 int64_t g = (int64_t)dev.sms * per_sm;
                 const int64_t needed = (n + b - 1) / b;
                 if (g > needed) g = needed;

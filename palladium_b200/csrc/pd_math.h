@@ -223,16 +223,8 @@ PD_HD float pd_exp2_scale(float r, int n) {
     return pd_mul(r, pd_u2f((uint32_t)(n + 127) << 23));
 }
 
-PD_HD float pd_powf(float x, float y) {
-    if (x != x || y != y) return x + y;
-    if (y == 0.0f) return 1.0f;
-    if (x < 0.0f) return pd_u2f(0x7FC00000u);
-    const float inf = pd_u2f(0x7F800000u);
-    if (x == 0.0f) return y > 0.0f ? 0.0f : inf;
-    if (x == inf) return y > 0.0f ? inf : 0.0f;
-    if (y == inf) return x > 1.0f ? inf : (x == 1.0f ? 1.0f : 0.0f);
-    if (y == -inf) return x > 1.0f ? 0.0f : (x == 1.0f ? 1.0f : inf);
-
+// log2(x) as a df32 value, for finite x > 0 (subnormals included).
+PD_HD pd_df32 pd_log2_df(float x) {
     uint32_t ix = pd_f2u(x);
     int e = 0;
     if (ix < 0x00800000u) {  // subnormal: scale up by 2^24 (exact)
@@ -272,9 +264,12 @@ PD_HD float pd_powf(float x, float y) {
     // T = e + P
     pd_df32 T = pd_two_sum((float)e, P.hi);
     T.lo = pd_add(T.lo, P.lo);
-    T = pd_fast_two_sum(T.hi, T.lo);
+    return pd_fast_two_sum(T.hi, T.lo);
+}
 
-    // W = y * T
+// 2^(y * T) for a df32 exponent factor T = log2(x): the second half of pd_powf.
+PD_HD float pd_exp2_of_product(float y, pd_df32 T) {
+    const float inf = pd_u2f(0x7F800000u);
     pd_df32 W = pd_two_prod(y, T.hi);
     W.lo = pd_fma(y, T.lo, W.lo);
 
@@ -295,6 +290,36 @@ PD_HD float pd_powf(float x, float y) {
     p = pd_fma(p, f, 6.93147181e-1f);            // ln2
     float r = pd_fma(p, f, 1.0f);
     return pd_exp2_scale(r, n);
+}
+
+// 1 when (x, y) needs one of pd_powf's domain rules instead of the log/exp path.
+PD_HD int pd_pow_is_special(float x, float y) {
+    const float inf = pd_u2f(0x7F800000u);
+    return (x != x) || (y != y) || y == 0.0f || !(x > 0.0f) || x == inf || y == inf || y == -inf;
+}
+
+PD_HD float pd_powf(float x, float y) {
+    if (x != x || y != y) return x + y;
+    if (y == 0.0f) return 1.0f;
+    if (x < 0.0f) return pd_u2f(0x7FC00000u);
+    const float inf = pd_u2f(0x7F800000u);
+    if (x == 0.0f) return y > 0.0f ? 0.0f : inf;
+    if (x == inf) return y > 0.0f ? inf : 0.0f;
+    if (y == inf) return x > 1.0f ? inf : (x == 1.0f ? 1.0f : 0.0f);
+    if (y == -inf) return x > 1.0f ? 0.0f : (x == 1.0f ? 1.0f : inf);
+    return pd_exp2_of_product(y, pd_log2_df(x));
+}
+
+// x**y1 and x**y2 with one logarithm: bit-identical to two pd_powf calls.
+PD_HD void pd_powf_pair(float x, float y1, float y2, float* r1, float* r2) {
+    if (pd_pow_is_special(x, y1) || pd_pow_is_special(x, y2)) {
+        *r1 = pd_powf(x, y1);
+        *r2 = pd_powf(x, y2);
+        return;
+    }
+    const pd_df32 T = pd_log2_df(x);
+    *r1 = pd_exp2_of_product(y1, T);
+    *r2 = pd_exp2_of_product(y2, T);
 }
 
 #endif  // PD_MATH_H_
