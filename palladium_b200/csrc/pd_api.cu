@@ -48,10 +48,11 @@ std::map<std::string, int64_t>& tuning() {
         {"lv_block", 0},             // 0 = choose from N
         {"vdp_variant", 1},          // 0 direct, 1 persistent warps with lane refill
         {"vdp_block", 128},
-        {"vdp_blocks_per_sm", 0},    // 0 = from the occupancy calculator
+        {"vdp_blocks_per_sm", 0},    // 0 = about 1024 resident threads per SM
         {"gbm_block", 256},
         {"gbm_blocks_per_sm", 0},
-        {"gs_variant", -1},          // -1 = vec4 when the shape allows, else per-cell
+        {"gs_variant", -1},          // -1 = best for the shape; 0 per cell, 1 vec4 (one step), 2 temporal blocking
+        {"gs_fuse", 4},              // steps fused per launch by variant 2 (2..4)
         {"df32_block", 128},
         {"time_kernels", 0},
     };
@@ -294,24 +295,39 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott: more than 2^31 cells per call");
             int variant = (int)knob("gs_variant");
             const bool vec_shape = (p->cols % 4 == 0) && p->cols >= 128 && vec_ok;
-            if (variant < 0) variant = vec_shape ? 1 : 0;
-            if (variant == 1 && !vec_shape) variant = 0;
+            if (variant < 0) variant = vec_shape ? (p->steps >= 2 ? 2 : 1) : 0;
+            if (variant >= 1 && !vec_shape) variant = 0;
+            int fuse = (int)knob("gs_fuse");
+            fuse = fuse < 2 ? 2 : (fuse > 4 ? 4 : fuse);
             plan->variant = variant;
-            plan->kernel = mt->kernel_ptr(family, variant);
+            int64_t launches = p->steps;
             if (variant == 0) {
+                plan->kernel = mt->kernel_ptr(family, 0);
                 plan->kernel_name = "pd_gs_cell_kernel";
                 plan->block[0] = 32; plan->block[1] = 8;
                 plan->grid[0] = (p->cols + 31) / 32;
                 plan->grid[1] = (rows_alloc + 7) / 8;
-            } else {
+            } else if (variant == 1 || p->steps < 2) {
+                plan->variant = vec_shape ? 1 : 0;
+                plan->kernel = mt->kernel_ptr(family, 1);
                 plan->kernel_name = "pd_gs_vec4_kernel";
                 plan->items = 4 * PD_GS_TILE_ROWS;
                 plan->block[0] = PD_GS_BLOCK;
                 plan->grid[0] = (p->cols / 4 + PD_GS_BLOCK - 1) / PD_GS_BLOCK;
                 plan->grid[1] = (rows_alloc + PD_GS_TILE_ROWS - 1) / PD_GS_TILE_ROWS;
+            } else {
+                const int k = p->steps < fuse ? (int)p->steps : fuse;
+                plan->variant = 10 + k;  // the kernel of the full-size launches
+                plan->kernel = mt->kernel_ptr(family, 10 + k);
+                plan->kernel_name = k == 4 ? "pd_gs_tb_kernel<4>" : k == 3 ? "pd_gs_tb_kernel<3>" : "pd_gs_tb_kernel<2>";
+                plan->items = 4;  // cells per thread per row
+                plan->block[0] = 256;
+                plan->grid[0] = (p->cols + 119) / 120;
+                plan->grid[1] = (rows_alloc + PD_GS_TB_ROWS - 1) / PD_GS_TB_ROWS;
+                launches = (p->steps + k - 1) / k;
             }
-            plan->launches = p->steps;
-            plan->scratch_bytes = p->steps >= 2 ? 2 * rows_alloc * p->cols * (int64_t)sizeof(float) : 0;
+            plan->launches = launches;
+            plan->scratch_bytes = launches >= 2 ? 2 * rows_alloc * p->cols * (int64_t)sizeof(float) : 0;
             return PD_OK;
         }
         case PD_FAMILY_LV_RK4_DF32:
@@ -560,17 +576,23 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             float* pong_v = scratch ? (float*)((char*)scratch + field_bytes) : nullptr;
             const float* src_u = (const float*)in[0];
             const float* src_v = (const float*)in[1];
-            // The last step must land in `out`: odd step counts start there.
-            bool to_out = (p->steps % 2) == 1;
-            for (int64_t s = 1; s <= p->steps; ++s) {
+            // Fused launches of k steps each (k = 1 for the one-step kernels); the
+            // last launch must land in `out`, so an odd launch count starts there.
+            const int fuse = plan.variant >= 12 ? plan.variant - 10 : 1;
+            bool to_out = (plan.launches % 2) == 1;
+            int64_t done = 0;
+            while (done < p->steps) {
+                const int k = (int)((p->steps - done) < fuse ? (p->steps - done) : fuse);
                 a.u = src_u; a.v = src_v;
                 a.uo = to_out ? ping_u : pong_u;
                 a.vo = to_out ? ping_v : pong_v;
                 if (p->halo == 0) { a.row_lo = 0; a.row_hi = rows_alloc; }
-                else { a.row_lo = (int)s; a.row_hi = rows_alloc - (int)s; }
-                PD_CUDA_TRY(mt->gray_scott(a, plan.variant, st));
+                else { a.row_lo = (int)(done + k); a.row_hi = rows_alloc - (int)(done + k); }
+                const int variant = k >= 2 ? 10 + k : (plan.variant >= 12 ? 1 : plan.variant);
+                PD_CUDA_TRY(mt->gray_scott(a, variant, st));
                 src_u = a.uo; src_v = a.vo;
                 to_out = !to_out;
+                done += k;
             }
             break;
         }

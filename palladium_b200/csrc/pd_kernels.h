@@ -102,5 +102,6 @@ cudaError_t pd_launch_int_chain(uint32_t* sink, int iters, int grid, int block, 
 // Gray-Scott geometry, shared by launcher and explain.
 static const int PD_GS_TILE_ROWS = 32;
 static const int PD_GS_BLOCK = 128;
+#define PD_GS_TB_ROWS 16  /* output rows per block of the temporally blocked kernel */
 
 #endif  // PD_KERNELS_H_

@@ -226,6 +226,45 @@ def test_gray_scott_safe_bit_exact(shape, steps):
     np.testing.assert_array_equal(got_v, want_v)
 
 
+@pytest.mark.parametrize("fuse", [2, 3, 4])
+@pytest.mark.parametrize("shape,steps", [((256, 1024), 9), ((96, 256), 4), ((33, 132), 5), ((40, 128), 7),
+                                         ((64, 360), 8), ((31, 244), 3), ((5, 128), 6)])
+def test_gray_scott_temporal_blocking_bit_exact(shape, steps, fuse):
+    """K fused steps in shared memory equal K single steps: tiles that overhang
+    the grid in both directions, periodic wrap through the halo, remainders."""
+    from palladium_b200 import _native
+
+    rows, cols = shape
+    rng = np.random.default_rng(8)
+    u = (1.0 - 0.5 * rng.random(shape)).astype(np.float32)
+    v = (0.25 * rng.random(shape)).astype(np.float32)
+    _native.set_tuning("gs_fuse", fuse)
+    try:
+        call = H.gs_solver(rows, cols, math_mode=SAFE, steps=steps)
+        assert call.explain(u, v).cuda_kernel.startswith("pd_gs_tb_kernel")
+        got_u, got_v = call(u, v)
+    finally:
+        _native.set_tuning("gs_fuse", 4)
+    want_u, want_v = oracle.gray_scott(u, v, steps=steps)
+    np.testing.assert_array_equal(got_u, want_u)
+    np.testing.assert_array_equal(got_v, want_v)
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2])
+def test_gray_scott_variants_agree(variant):
+    from palladium_b200 import _native
+
+    u, v = W.gray_scott_initial_state(256, seed=11, patches=8)
+    _native.set_tuning("gs_variant", variant)
+    try:
+        got_u, got_v = H.gs_solver(256, 256, math_mode=SAFE, steps=6)(u, v)
+    finally:
+        _native.set_tuning("gs_variant", -1)
+    want_u, want_v = oracle.gray_scott(u, v, steps=6)
+    np.testing.assert_array_equal(got_u, want_u)
+    np.testing.assert_array_equal(got_v, want_v)
+
+
 def test_gray_scott_patches_cross_the_seam():
     size = 256
     u, v = W.gray_scott_initial_state(size, seed=11, patches=8, patch=32)

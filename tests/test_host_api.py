@@ -70,7 +70,9 @@ def test_explain_other_families():
     d = H.vdp_solver(5000, outputs=6).explain(*[H.shaped(5000)] * 3)
     assert d.cuda_kernel == "pd_vdp_refill_kernel" and d.scratch_bytes > 0
     d = H.gs_solver(256, 256, steps=10).explain(H.shaped(256, 256), H.shaped(256, 256))
-    assert d.cuda_kernel == "pd_gs_vec4_kernel" and d.launches == 10 and d.scratch_bytes == 2 * 256 * 256 * 4
+    assert d.cuda_kernel == "pd_gs_tb_kernel<4>" and d.launches == 3 and d.scratch_bytes == 2 * 256 * 256 * 4
+    d = H.gs_solver(256, 256, steps=1).explain(H.shaped(256, 256), H.shaped(256, 256))
+    assert d.cuda_kernel == "pd_gs_vec4_kernel" and d.launches == 1 and d.scratch_bytes == 0
     d = H.gs_solver(30, 50).explain(H.shaped(30, 50), H.shaped(30, 50))
     assert d.cuda_kernel == "pd_gs_cell_kernel"
     d = H.gbm_solver(1 << 16, with_sums=True).explain(H.shaped(2, dtype=np.uint32))
