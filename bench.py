@@ -258,7 +258,10 @@ def main():
     nominal_peak = 2.0 * FP32_LANES_PER_SM * SM_COUNT * (clk["sm_max_mhz"] or 1965) * 1e6
     roofline = {
         "bound": "fp32_fma", "achieved": achieved_flops / 1e12, "peak": fma_peak / 1e12, "unit": "TFLOP/s",
-        "frac": achieved_flops / fma_peak, "traffic": None,
+        "frac": achieved_flops / fma_peak,
+        # ncu on an N = 1 212 416 capture: dram__bytes_read = 24 B x N exactly (each input array read
+        # once), writes 8 B x N once evicted from L2; scaled by N for this launch.
+        "traffic": 32 * n,
         "peak_source": "FMA-chain microbenchmark of this library, measured in this run on this GPU "
                        "(MEASURED_PEAKS.json holds no fp32 figure)",
         "nominal_peak": nominal_peak / 1e12, "frac_of_nominal": achieved_flops / nominal_peak,
