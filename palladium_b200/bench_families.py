@@ -202,6 +202,46 @@ def quick_summary() -> dict:
     return out
 
 
+def full_configs(fma_peak: float, int_peak: float) -> dict:
+    """Each benchmark configuration once at its full size on one GPU
+    (`bench.py --workload full`): wall time of the whole job on the device."""
+    import torch
+
+    from . import cuda_call_jit, families
+    from . import workloads as W
+
+    out = {"metric": "full_configurations", "value": None, "unit": "s", "scaling": "weak", "ms_per_step": None,
+           "config": {"workload": "every benchmark configuration at full size, one GPU"}}
+    r = bench_vdp(W.VDP_CONFIG["n"], "relaxed", warmup=1, iters=1, fma_peak=fma_peak)
+    out["vdp_bs32_relaxed_1M"] = {"seconds": r["ms"] / 1e3, "attempts_per_s": r["attempts_per_s"]}
+    r = bench_vdp(W.VDP_CONFIG["n"], "safe", warmup=1, iters=1, fma_peak=fma_peak)
+    out["vdp_bs32_safe_1M"] = {"seconds": r["ms"] / 1e3, "attempts_per_s": r["attempts_per_s"]}
+    r = bench_gbm(W.GBM_CONFIG["n"], "fast", warmup=1, iters=1, int_peak=int_peak)
+    out["gbm_2^26"] = {"seconds": r["ms"] / 1e3, "path_steps_per_s": r["path_steps_per_s"], "price": r["price"],
+                       "stderr": r["stderr"], "black_scholes": r["black_scholes"]}
+    r = bench_gray_scott(W.GRAY_SCOTT_CONFIG["size"], W.GRAY_SCOTT_CONFIG["steps"], "fast", warmup=0, iters=1)
+    out["gray_scott_8192_10000_steps"] = {"seconds": r["ms"] / 1e3, "us_per_step": r["ms_per_step"] * 1e3,
+                                          "algorithmic_gbs": r["algorithmic_gbs"]}
+    cfg = W.KEPLER_CONFIG
+    n, chunk = cfg["n"], 1000
+    call = cuda_call_jit(families.kepler_rk4_df32(dt=cfg["dt"], gm=cfg["gm"], steps=chunk), grid=(n,),
+                         out_shape=tuple(_shaped((n,)) for _ in range(8)), math_mode="safe")
+    _, pairs = W.kepler_ensemble(n)
+    dev = [torch.from_numpy(a).cuda() for a in pairs]
+    dev = list(call(*dev))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(cfg["steps"] // chunk):
+        dev = list(call(*dev))
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / 1e3
+    out["kepler_df32_1M_100000_steps"] = {"seconds": sec, "trajectory_steps_per_s": float(n) * cfg["steps"] / sec,
+                                          "launches": cfg["steps"] // chunk}
+    return out
+
+
 # ----------------------------------------------------------------------------- as the main workload
 def run(args, rank: int, local_rank: int, world: int, barrier, max_over_ranks) -> None:
     import torch
@@ -293,6 +333,8 @@ def run(args, rank: int, local_rank: int, world: int, barrier, max_over_ranks) -
                      "roofline": {"bound": "fp32_fma", "achieved": r["trajectory_steps_per_s"] * DF32_KEPLER_FLOPS / 1e12,
                                   "peak": fma_peak / 1e12, "unit": "TFLOP/s", "frac": r.get("frac_of_fp32_peak"),
                                   "traffic": None}})
+    elif name == "full":
+        line.update(full_configs(fma_peak, int_peak))
     else:
         raise SystemExit(f"unknown workload {name!r}")
     if rank == 0:
