@@ -59,7 +59,8 @@ typedef enum pd_family {
     PD_FAMILY_LV_RK4_DF32 = 4,   /* lv_rk4_df32, examples/05_df32_precision.py:27-80 */
     PD_FAMILY_KEPLER_RK4_DF32 = 5, /* same df32 RK4 scheme on the two-body problem */
     PD_FAMILY_THREEFRY_BITS = 6, /* random_bits / uniform / fold_in, src/palladium/emit/rules.py:168-201 */
-    PD_FAMILY_COUNT = 7
+    PD_FAMILY_GBM_PCG = 7,       /* gbm_paths with pcg_hash, the hand-written kernel GBM_MSL, examples/03_sde_montecarlo.py:34-70 */
+    PD_FAMILY_COUNT = 8
 } pd_family;
 
 /* ---- per-family parameter blocks (passed by pointer + sizeof) ------------ */
@@ -88,6 +89,9 @@ typedef struct pd_vdp_bs32_params {
 /* in:  key data (2) u32.   out[0]: (N) f32 payoff (output_kind 0) or terminal
  * price (output_kind 1); optional out[1]: (2) f64 = {sum payoff, sum payoff^2}
  * over this call's paths.  Path i uses RNG stream fold_in(key, path_offset+i). */
+/* PD_FAMILY_GBM_PCG takes the same block and no input: path i, step s draws
+ * u1 = uniform01(2*c), u2 = uniform01(2*c + 1) with c = (path_offset + i) * steps + s
+ * in 32-bit arithmetic (examples/03_sde_montecarlo.py:60-62). */
 typedef struct pd_gbm_params {
     double s0, strike, r, sigma, t;
     int64_t steps;
@@ -125,7 +129,8 @@ typedef struct pd_kepler_rk4_df32_params {
  * op 0: out (N) u32 = random_bits(key, (N,))
  * op 1: out (N) f32 = uniform(key, (N,))
  * op 2: out (M,2) u32 = key_data(fold_in(key, data[m]))
- * op 3: out (G,count) f32, row g = uniform(fold_in(key, g), (count,)) */
+ * op 3: out (G,count) f32, row g = uniform(fold_in(key, g), (count,))
+ * op 4: out (N) u32 = pcg_hash(i)   (key is ignored) */
 typedef struct pd_threefry_params {
     int64_t op;
     int64_t count;

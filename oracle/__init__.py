@@ -180,6 +180,25 @@ def gbm(key, n: int, *, s0: float, strike: float, r: float, sigma: float, t: flo
     return terminal, payoff
 
 
+def pcg_hash(n: int) -> np.ndarray:
+    out = np.empty(n, np.uint32)
+    lib().orc_pcg_hash(_i64(n), _p(out, _u32p))
+    return out
+
+
+def gbm_pcg(n: int, *, s0: float, strike: float, r: float, sigma: float, t: float, steps: int, path_offset: int = 0):
+    """The hand-written kernel's paths; scalars as `run_handwritten` forms them
+    (examples/03_sde_montecarlo.py:80-89).  Returns (terminal, payoff)."""
+    dt = t / steps
+    drift_dt = np.float32((r - sigma**2 / 2) * dt)
+    vol_sqdt = np.float32(sigma * np.sqrt(dt))
+    terminal, payoff = np.empty(n, np.float32), np.empty(n, np.float32)
+    lib().orc_gbm_pcg(_i64(n), _i64(path_offset), _i64(steps), ctypes.c_float(s0), ctypes.c_float(strike),
+                      ctypes.c_float(float(drift_dt)), ctypes.c_float(float(vol_sqdt)), _p(terminal, _f32p),
+                      _p(payoff, _f32p))
+    return terminal, payoff
+
+
 def black_scholes_call(s0: float, k: float, t: float, r: float, sigma: float) -> float:
     """Closed form the Monte Carlo price is checked against (examples/03:73-76)."""
     from math import erf, exp, log, sqrt

@@ -246,6 +246,38 @@ ORC_API void orc_gbm(int64_t n, const uint32_t* key, int64_t path_offset, int64_
 }
 
 /* ------------------------------------------------------------------------- */
+/* The hand-written GBM kernel with pcg_hash (examples/03_sde_montecarlo.py:34-70) */
+/* ------------------------------------------------------------------------- */
+static uint32_t pcg_hash(uint32_t v) {
+    uint32_t state = v * 747796405u + 2891336453u;
+    uint32_t word = ((state >> ((state >> 28u) + 4u)) ^ state) * 277803737u;
+    return (word >> 22u) ^ word;
+}
+static float pcg_uniform01(uint32_t v) { return ((float)pcg_hash(v) + 0.5f) * 2.3283064e-10f; }
+
+ORC_API void orc_pcg_hash(int64_t n, uint32_t* out) {
+    for (int64_t i = 0; i < n; ++i) out[i] = pcg_hash((uint32_t)i);
+}
+
+ORC_API void orc_gbm_pcg(int64_t n, int64_t path_offset, int64_t steps, float s0, float strike, float drift_dt,
+                         float vol_sqdt, float* terminal, float* payoff) {
+#pragma omp parallel for schedule(static)
+    for (int64_t p = 0; p < n; ++p) {
+        const uint32_t tid = (uint32_t)(path_offset + p);
+        float s = s0;
+        for (uint32_t i = 0; i < (uint32_t)steps; ++i) {
+            uint32_t ctr = tid * (uint32_t)steps + i;
+            float u1 = pcg_uniform01(2u * ctr);
+            float u2 = pcg_uniform01(2u * ctr + 1u);
+            float z = sqrtf(-2.0f * logf(u1)) * cosf(6.2831853f * u2);
+            s *= expf(drift_dt + vol_sqdt * z);
+        }
+        if (terminal) terminal[p] = s;
+        if (payoff) { float d = s - strike; payoff[p] = d > 0.0f ? d : 0.0f; }
+    }
+}
+
+/* ------------------------------------------------------------------------- */
 /* Gray-Scott stencil step (examples/04_reaction_diffusion.py:61-74), periodic  */
 /* ------------------------------------------------------------------------- */
 static void gray_scott_step(int64_t rows, int64_t cols, const float* u_, const float* v_, float* uo, float* vo,

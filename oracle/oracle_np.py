@@ -140,3 +140,16 @@ def gbm(key, n: int, *, s0, strike, r, sigma, t, steps: int, path_offset: int = 
         z = np.sqrt(F32(-2.0) * np.log(u1)) * np.cos(two_pi * u2)
         s = s * np.exp(drift_dt + vol_sqdt * z)
     return s, np.maximum(s - F32(strike), F32(0.0))
+
+
+def pcg_hash(v) -> np.ndarray:
+    """examples/03_sde_montecarlo.py:38-43 on uint32 arrays."""
+    with np.errstate(over="ignore"):
+        v = np.asarray(v, U32)
+        state = v * U32(747796405) + U32(2891336453)
+        word = ((state >> ((state >> U32(28)) + U32(4))) ^ state) * U32(277803737)
+        return (word >> U32(22)) ^ word
+
+
+def pcg_uniform01(v) -> np.ndarray:
+    return (pcg_hash(v).astype(F32) + F32(0.5)) * F32(2.3283064e-10)

@@ -30,6 +30,7 @@ from .families import BlockInfo, Family, KernelSpec, trace
 from .ffi import FfiCallable, cuda_call_jit
 from .interpret import interpret_callable, register_interpret_provider
 from .math_mode import MathMode
+from .stepping import Stepper
 
 __all__ = [
     "BlockInfo",
@@ -44,6 +45,7 @@ __all__ = [
     "MathMode",
     "PalladiumError",
     "PendingResult",
+    "Stepper",
     "TraceError",
     "UnsupportedPrimitiveError",
     "bind",

@@ -59,6 +59,7 @@ FAMILY_IDS = {
     "lv_rk4_df32": 4,
     "kepler_rk4_df32": 5,
     "threefry_bits": 6,
+    "gbm_pcg": 7,
 }
 
 _i64 = ctypes.c_int64

@@ -128,6 +128,23 @@ def bench_gbm(n: int, math_mode="fast", warmup: int = 1, iters: int = 3, int_pea
     return res
 
 
+def bench_gbm_pcg(n: int, math_mode="fast", warmup: int = 1, iters: int = 3) -> dict:
+    """The reference's hand-written variant (pcg_hash), at its own constants
+    (examples/03_sde_montecarlo.py:30-32)."""
+    from . import cuda_call_jit, families
+
+    call = cuda_call_jit(families.gbm_pcg(), grid=(n,), out_shape=(_shaped((n,)), _shaped((2,), np.float64)),
+                         math_mode=math_mode)
+    out, sums = call.on_device()
+    ms = _time(lambda: call.on_device(), warmup, iters)
+    s1, s2 = (float(v) for v in sums.cpu())
+    disc = float(np.exp(-0.03))
+    mean = s1 / n
+    return {"workload": "GBM Monte Carlo, pcg_hash (the reference's hand-written kernel)", "paths": n, "steps": 256,
+            "math_mode": str(math_mode), "ms": ms, "path_steps_per_s": float(n) * 256 / (ms * 1e-3),
+            "price": disc * mean, "stderr": disc * float(np.sqrt(max(s2 / n - mean * mean, 0.0) / n))}
+
+
 def bench_gray_scott(size: int, steps: int, math_mode="fast", warmup: int = 1, iters: int = 3) -> dict:
     import torch
 
@@ -196,6 +213,7 @@ def quick_summary() -> dict:
     out["vdp_bs32"] = bench_vdp(1 << 18, "relaxed", fma_peak=fma_peak)
     out["vdp_bs32_safe"] = bench_vdp(1 << 18, "safe", fma_peak=fma_peak)
     out["gbm"] = bench_gbm(1 << 22, "fast", int_peak=int_peak)
+    out["gbm_pcg"] = bench_gbm_pcg(1 << 22, "fast")
     out["gray_scott"] = bench_gray_scott(8192, 40, "fast")
     out["kepler_df32"] = bench_kepler(1 << 20, 100, fma_peak=fma_peak)
     out["lv_df32"] = bench_lv_df32(1 << 20, 100, fma_peak=fma_peak)

@@ -250,17 +250,18 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
             }
             return PD_OK;
         }
+        case PD_FAMILY_GBM_PCG:
         case PD_FAMILY_GBM_THREEFRY: {
             const pd_gbm_params* p;
-            int rc = get_params(params, params_bytes, &p, "gbm_threefry", err, err_cap);
+            int rc = get_params(params, params_bytes, &p, "gbm", err, err_cap);
             if (rc) return rc;
             if (p->steps < 0 || p->steps > (1 << 30))
-                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gbm_threefry: steps out of range");
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gbm: steps out of range");
             if (p->path_offset < 0 || p->path_offset + n > ((int64_t)1 << 32))
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
                             "gbm_threefry: path indices must fit in 32 bits (fold_in takes a uint32)");
             int b = req_block ? req_block : (int)knob("gbm_block");
-            plan->kernel_name = "pd_gbm_kernel";
+            plan->kernel_name = family == PD_FAMILY_GBM_PCG ? "pd_gbm_kernel<pcg>" : "pd_gbm_kernel<threefry>";
             plan->kernel = mt->kernel_ptr(family, 0);
             int per_sm = (int)knob("gbm_blocks_per_sm");
             if (!per_sm) per_sm = dev.present ? occupancy_blocks(plan->kernel, b) : 0;
@@ -358,8 +359,8 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
             const pd_threefry_params* p;
             int rc = get_params(params, params_bytes, &p, "threefry_bits", err, err_cap);
             if (rc) return rc;
-            if (p->op < 0 || p->op > 3)
-                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "threefry_bits: op must be 0..3");
+            if (p->op < 0 || p->op > 4)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "threefry_bits: op must be 0..4");
             if (p->op == 3 && p->count <= 0)
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "threefry_bits: count must be positive");
             const int64_t total = p->op == 3 ? n * p->count : n;
@@ -415,8 +416,9 @@ int expected_sizes(int family, const void* params, const int64_t grid[3], std::v
             else { out->assign(3, 4 * n); (*out)[0] = 8 * n; }
             return PD_OK;
         }
+        case PD_FAMILY_GBM_PCG:
         case PD_FAMILY_GBM_THREEFRY:
-            in->assign(1, 8);
+            if (family == PD_FAMILY_GBM_THREEFRY) in->assign(1, 8); else in->clear();
             out->assign(1, 4 * n);
             if (n_out_given == 2) out->push_back(16);
             return PD_OK;
@@ -535,10 +537,12 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             PD_CUDA_TRY(mt->vdp_bs32(a, plan.variant, (int)plan.grid[0], b, st));
             break;
         }
+        case PD_FAMILY_GBM_PCG:
         case PD_FAMILY_GBM_THREEFRY: {
             const pd_gbm_params* p = static_cast<const pd_gbm_params*>(params);
             PdGbmArgs a;
-            a.key = (const uint32_t*)in[0];
+            a.rng = family == PD_FAMILY_GBM_PCG ? 1 : 0;
+            a.key = a.rng == 0 ? (const uint32_t*)in[0] : nullptr;
             a.out = (float*)out[0];
             a.block_partials = (n_out == 2) ? (double*)scratch : nullptr;
             a.n = n; a.path_offset = (uint32_t)p->path_offset; a.steps = (int)p->steps;
@@ -546,7 +550,9 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             const double dt = p->t / (double)(p->steps > 0 ? p->steps : 1);
             a.s0 = (float)p->s0; a.strike = (float)p->strike;
             a.drift_dt = (float)((p->r - p->sigma * p->sigma / 2.0) * dt);
-            a.vol_sqdt = (float)p->sigma * sqrtf((float)dt);
+            // Threefry kernel: f32(sigma) * sqrt_f32(f32(dt)) (examples/03:100); the hand-written
+            // kernel receives np.float32(sigma * np.sqrt(dt)) (examples/03:88).
+            a.vol_sqdt = a.rng == 0 ? (float)p->sigma * sqrtf((float)dt) : (float)(p->sigma * sqrt(dt));
             if (n_out == 2 && !aligned(out[1], 8))
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output 1: float64 sums must be 8-byte aligned");
             PD_CUDA_TRY(mt->gbm(a, (int)plan.grid[0], b, st));
@@ -733,7 +739,7 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
     // count (the RNG key) is uploaded once and the chunk streams wait for it.
     const bool per_item_family = family == PD_FAMILY_LV_RK4 || family == PD_FAMILY_VDP_BS32 ||
                                  family == PD_FAMILY_LV_RK4_DF32 || family == PD_FAMILY_KEPLER_RK4_DF32 ||
-                                 (family == PD_FAMILY_GBM_THREEFRY && n_out == 1);
+                                 ((family == PD_FAMILY_GBM_THREEFRY || family == PD_FAMILY_GBM_PCG) && n_out == 1);
     const int64_t n = grid ? grid[0] : 0;
     const int64_t kMinChunked = (int64_t)1 << 18;
     bool chunked = per_item_family && n >= kMinChunked && params && params_bytes <= 256;
@@ -787,7 +793,7 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
                 c_out[i] = (char*)hs.slots[n_in + i].ptr + (size_t)lo * out_item[i];
                 c_out_bytes[i] = (size_t)len * out_item[i];
             }
-            if (family == PD_FAMILY_GBM_THREEFRY) {
+            if (family == PD_FAMILY_GBM_THREEFRY || family == PD_FAMILY_GBM_PCG) {
                 pd_gbm_params gp;
                 memcpy(&gp, params, sizeof(gp));
                 gp.path_offset += lo;

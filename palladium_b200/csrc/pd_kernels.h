@@ -38,6 +38,7 @@ struct PdGbmArgs {
     uint32_t path_offset;
     int steps;
     int output_kind;
+    int rng;  // 0 Threefry keyed by `key`, 1 pcg_hash of a running counter
     float s0, strike, drift_dt, vol_sqdt;
 };
 

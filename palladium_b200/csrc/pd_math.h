@@ -127,6 +127,26 @@ PD_HD float pd_bits_to_uniform(uint32_t bits) {
 }
 
 // ---------------------------------------------------------------------------
+// pcg_hash counter RNG of the reference's hand-written GBM kernel
+// (examples/03_sde_montecarlo.py:38-49): one multiply-add, a data-dependent
+// shift-xor, one multiply, one shift-xor; the uniform is (hash + 0.5) * 2^-32,
+// an open-interval value that is safe under log().
+// ---------------------------------------------------------------------------
+PD_HD uint32_t pd_pcg_hash(uint32_t v) {
+    const uint32_t state = v * 747796405u + 2891336453u;
+    const uint32_t word = ((state >> ((state >> 28) + 4u)) ^ state) * 277803737u;
+    return (word >> 22) ^ word;
+}
+PD_HD float pd_pcg_uniform01(uint32_t v) {
+#if defined(__CUDA_ARCH__)
+    const float h = __uint2float_rn(pd_pcg_hash(v));
+#else
+    const float h = (float)pd_pcg_hash(v);
+#endif
+    return pd_mul(pd_add(h, 0.5f), 2.3283064365386963e-10f);  // 2^-32
+}
+
+// ---------------------------------------------------------------------------
 // df32: value = hi + lo with |lo| <= ulp(hi)/2.
 // ---------------------------------------------------------------------------
 typedef struct pd_df32 { float hi, lo; } pd_df32;

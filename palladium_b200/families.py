@@ -30,6 +30,7 @@ __all__ = [
     "BlockInfo",
     "Family",
     "KernelSpec",
+    "gbm_pcg",
     "gbm_threefry",
     "gray_scott",
     "kepler_rk4_df32",
@@ -134,6 +135,18 @@ def gbm_threefry(s0: float = 100.0, strike: float = 105.0, r: float = 0.03, sigm
                                        path_offset=int(path_offset)), pallas_fn)
 
 
+def gbm_pcg(s0: float = 100.0, strike: float = 105.0, r: float = 0.03, sigma: float = 0.2, t: float = 1.0,
+            steps: int = 256, output: str = "payoff", path_offset: int = 0) -> Family:
+    """The reference's hand-written GBM kernel (`GBM_MSL`, examples/03_sde_montecarlo.py:34-70):
+    same model as `gbm_threefry` with the cheap `pcg_hash` counter RNG, one hash
+    per uniform.  grid=(N,), no inputs, one (N,) float32 output (payoff or
+    terminal price) and an optional (2,) float64 output of payoff sums."""
+    if output not in ("payoff", "terminal"):
+        raise TraceError(f"gbm_pcg: output must be 'payoff' or 'terminal', got {output!r}")
+    return Family("gbm_pcg", dict(s0=float(s0), strike=float(strike), r=float(r), sigma=float(sigma), t=float(t),
+                                  steps=int(steps), output=output, path_offset=int(path_offset)))
+
+
 def gray_scott(du: float = 0.16, dv: float = 0.08, f: float = 0.035, k: float = 0.065, dt: float = 1.0,
                steps: int = 1, halo: int = 0, pallas_fn: Callable | None = None) -> Family:
     """Gray-Scott 5-point stencil (examples/04_reaction_diffusion.py:61-74; constants :35).
@@ -162,8 +175,10 @@ def threefry_bits(op: str = "bits", count: int = 1) -> Family:
     """The RNG primitives on their own (src/palladium/emit/rules.py:168-201):
     op "bits": (N,) uint32 = random_bits(key, (N,)); "uniform": (N,) float32;
     "fold_in": inputs key and (M,) uint32 data, output (M, 2) uint32 key data;
-    "fold_uniform": (G, count) float32, row g = uniform(fold_in(key, g), (count,))."""
-    ops = {"bits": 0, "uniform": 1, "fold_in": 2, "fold_uniform": 3}
+    "fold_uniform": (G, count) float32, row g = uniform(fold_in(key, g), (count,));
+    "pcg": (N,) uint32 = pcg_hash(i), the hash of examples/03_sde_montecarlo.py:38-43
+    (the key input is ignored)."""
+    ops = {"bits": 0, "uniform": 1, "fold_in": 2, "fold_uniform": 3, "pcg": 4}
     if op not in ops:
         raise TraceError(f"threefry_bits: op must be one of {sorted(ops)}, got {op!r}")
     return Family("threefry_bits", dict(op=op, op_code=ops[op], count=int(count)))
@@ -299,12 +314,15 @@ def trace(family: Family, call_kwargs: dict[str, Any], *args) -> KernelSpec:
         params = _native.VdpBs32Params(c["t1"], c["rtol"], c["atol"], c["dt0"], c["pcoeff"], c["icoeff"],
                                        c["safety"], c["factor_min"], c["factor_max"], c["error_order"],
                                        c["max_steps"], layout)
-    elif name == "gbm_threefry":
+    elif name in ("gbm_threefry", "gbm_pcg"):
         if len(grid) != 1:
             raise TraceError(f"{name}: grid must be (N,), got {grid}")
         n = grid[0]
-        inputs = (BlockInfo((2,), (2,), U32),)
-        blocks_in = [((2,), lambda i: (0,))]
+        if name == "gbm_threefry":
+            inputs = (BlockInfo((2,), (2,), U32),)
+            blocks_in = [((2,), lambda i: (0,))]
+        else:
+            inputs, blocks_in = (), []
         outputs = (vec(n),)
         blocks_out = [_per_item(n)]
         if len(outs) == 2:
@@ -339,7 +357,7 @@ def trace(family: Family, call_kwargs: dict[str, Any], *args) -> KernelSpec:
         n = grid[0]
         key = BlockInfo((2,), (2,), U32)
         op = c["op"]
-        if op == "bits":
+        if op in ("bits", "pcg"):
             inputs, outputs = (key,), (vec(n, U32),)
         elif op == "uniform":
             inputs, outputs = (key,), (vec(n),)

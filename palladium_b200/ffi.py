@@ -139,10 +139,16 @@ class FfiCallable:
         spec, bound = self._entry(shapes)
         torch_dtype = {"float32": torch.float32, "int32": torch.int32, "uint32": torch.uint32,
                        "float64": torch.float64}
-        outs = [torch.empty(info.array_shape, dtype=torch_dtype[info.dtype.name], device=args[0].device)
+        device = args[0].device if args else torch.device("cuda", torch.cuda.current_device())
+        outs = [torch.empty(info.array_shape, dtype=torch_dtype[info.dtype.name], device=device)
                 for info in spec.outputs]
         bound.launch_device(list(args), outs)
         return outs[0] if len(outs) == 1 else tuple(outs)
+
+    def on_device(self, *args):
+        """Stream-ordered launch returning torch CUDA tensors, also for families
+        without inputs (where `__call__` cannot tell a device call from a host call)."""
+        return self._call_torch(args)
 
     # ---- host buffers: the XLA:CPU handler contract -----------------------------
     def _call_host(self, args):

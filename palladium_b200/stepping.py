@@ -1,0 +1,125 @@
+"""Device-resident stepping: many launches of one call with the state kept on
+the GPU, one wait at the end.
+
+The reference's stencil example drives its kernel this way by hand: two buffer
+pairs on the device, one dispatch per step appended to a single batch with the
+pairs swapped, one commit, one wait, and `batch.gpu_time` for the device-side
+duration (examples/04_reaction_diffusion.py:92-109); its `launch()` / `wait()`
+pair is the general form (src/palladium/dispatch.py:129-194).  `Stepper` is that
+pattern as an object, for any call whose leading outputs are the next call's
+leading inputs (the Gray-Scott fields, a df32 orbit state, the (x, y) state of
+an ODE ensemble whose parameters stay fixed).
+"""
+
+from __future__ import annotations
+
+from collections.abc import Sequence
+
+import numpy as np
+
+from .dispatch import BoundKernel, _require_cuda
+from .errors import DispatchError
+
+__all__ = ["Stepper"]
+
+
+class Stepper:
+    """Keeps a call's operands on the device and re-launches it in place.
+
+    Parameters
+    ----------
+    call : CudaCallable or FfiCallable
+        The call to repeat (e.g. `cuda_call(families.gray_scott(steps=4), ...)`:
+        every launch then advances four steps).
+    *arrays : numpy arrays
+        Initial inputs, uploaded once.
+    feedback : sequence of int, optional
+        `feedback[k]` is the input slot that output k feeds for the next launch;
+        by default output k feeds input k.  Inputs that no output feeds keep
+        their initial values (per-trajectory parameters).
+    """
+
+    def __init__(self, call, *arrays, feedback: Sequence[int] | None = None):
+        torch = _require_cuda()
+        arrs = [np.ascontiguousarray(np.asarray(a)) for a in arrays]
+        self._bound: BoundKernel = self._bind(call, arrs)
+        spec = self._bound.spec
+        self._bound._checked(arrs)
+        n_out = len(spec.outputs)
+        self._feedback = list(range(n_out)) if feedback is None else [int(i) for i in feedback]
+        if len(self._feedback) != n_out:
+            raise DispatchError(f"feedback must name one input slot per output ({n_out}), got {len(self._feedback)}")
+        for k, slot in enumerate(self._feedback):
+            if not 0 <= slot < len(spec.inputs):
+                raise DispatchError(f"feedback[{k}] = {slot} is not an input slot")
+            a, b = spec.outputs[k], spec.inputs[slot]
+            if a.array_shape != b.array_shape or a.dtype != b.dtype:
+                raise DispatchError(f"output {k} ({a.array_shape} {a.dtype}) cannot feed input {slot} "
+                                    f"({b.array_shape} {b.dtype})")
+        self._stream = torch.cuda.Stream()
+        with torch.cuda.stream(self._stream):
+            self._inputs = [torch.from_numpy(a.reshape(-1).view(np.uint8).copy()).cuda() if a.nbytes
+                            else torch.empty(1, dtype=torch.uint8, device="cuda") for a in arrs]
+            sizes = [max(int(np.prod(o.array_shape)) * o.dtype.itemsize, 1) for o in spec.outputs]
+            # two output sets: a launch never writes the buffers it reads
+            self._spare = [[torch.empty(s, dtype=torch.uint8, device="cuda") for s in sizes] for _ in range(2)]
+        self._which = 0
+        self._outputs = None
+        self._start = torch.cuda.Event(enable_timing=True)
+        self._end = torch.cuda.Event(enable_timing=True)
+        self._timed = False
+        self.launches = 0
+
+    @staticmethod
+    def _bind(call, arrs) -> BoundKernel:
+        if hasattr(call, "_bound"):            # CudaCallable
+            return call._bound(arrs)
+        if hasattr(call, "_entry"):            # FfiCallable
+            return call._entry(tuple((a.shape, a.dtype.name) for a in arrs))[1]
+        raise DispatchError("Stepper needs a call built by cuda_call or cuda_call_jit")
+
+    def advance(self, launches: int = 1) -> "Stepper":
+        """Enqueue `launches` launches, each consuming the previous one's
+        outputs; returns without waiting."""
+        torch = _require_cuda()
+        with torch.cuda.stream(self._stream):
+            if not self._timed:
+                self._start.record(self._stream)
+                self._timed = True
+            for _ in range(int(launches)):
+                # Alternate between the two output sets: after this launch the fed
+                # inputs alias set `which`, so the next launch must write the other.
+                outs = self._spare[self._which]
+                self._bound.launch_device(self._inputs, outs, stream=self._stream)
+                for k, slot in enumerate(self._feedback):
+                    self._inputs[slot] = outs[k]
+                self._which = 1 - self._which
+                self._outputs = outs
+                self.launches += 1
+            self._end.record(self._stream)
+        return self
+
+    def wait(self) -> "Stepper":
+        self._end.synchronize()
+        return self
+
+    @property
+    def gpu_time(self) -> float:
+        """Seconds the device spent between the first `advance` and the last
+        launch so far (the analogue of `batch.gpu_time`)."""
+        if not self._timed:
+            return 0.0
+        self._end.synchronize()
+        return self._start.elapsed_time(self._end) / 1e3
+
+    def read(self):
+        """Wait, then return the latest outputs as NumPy arrays."""
+        if self._outputs is None:
+            raise DispatchError("nothing has been launched yet")
+        self.wait()
+        spec = self._bound.spec
+        outs = []
+        for t, info in zip(self._outputs, spec.outputs):
+            nbytes = int(np.prod(info.array_shape)) * info.dtype.itemsize
+            outs.append(t[:nbytes].cpu().numpy().view(info.dtype).reshape(info.array_shape))
+        return outs[0] if len(outs) == 1 else tuple(outs)

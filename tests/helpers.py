@@ -46,6 +46,13 @@ def gbm_solver(n, with_sums=False, call=None, math_mode=pd.MathMode.FAST, **cons
                                   out_specs=out_specs, out_shape=out_shape, math_mode=math_mode)
 
 
+def gbm_pcg_solver(n, with_sums=False, call=None, math_mode=pd.MathMode.FAST, **constants):
+    """The hand-written variant: no inputs (examples/03_sde_montecarlo.py:78-93)."""
+    fam = families.gbm_pcg(**constants)
+    out_shape = (shaped(n), shaped(2, dtype=np.float64)) if with_sums else shaped(n)
+    return (call or pd.cuda_call)(fam, grid=(n,), out_shape=out_shape, math_mode=math_mode)
+
+
 def gs_solver(rows, cols, call=None, math_mode=pd.MathMode.FAST, **constants):
     """examples/04_reaction_diffusion.py:77-88."""
     fam = families.gray_scott(**constants)
@@ -64,7 +71,7 @@ def kepler_solver(n, call=None, **constants):
 
 def threefry_solver(op, n, count=1, call=None):
     fam = families.threefry_bits(op, count)
-    if op == "bits":
+    if op in ("bits", "pcg"):
         out = shaped(n, dtype=np.uint32)
     elif op == "uniform":
         out = shaped(n)

@@ -35,6 +35,16 @@ def interpret(family, pallas_kwargs, *args, pow_flavour="pd"):
             p64 = payoff.astype(np.float64)
             return first, np.array([p64.sum(), (p64 * p64).sum()])
         return first
+    if name == "gbm_pcg":
+        grid = pallas_kwargs["grid"]
+        n = int(grid[0] if isinstance(grid, (tuple, list)) else grid)
+        terminal, payoff = oracle.gbm_pcg(n, s0=c["s0"], strike=c["strike"], r=c["r"], sigma=c["sigma"], t=c["t"],
+                                          steps=c["steps"], path_offset=c["path_offset"])
+        first = payoff if c["output"] == "payoff" else terminal
+        if n_out == 2:
+            p64 = payoff.astype(np.float64)
+            return first, np.array([p64.sum(), (p64 * p64).sum()])
+        return first
     if name == "gray_scott":
         if c["halo"]:
             raise NotImplementedError("the oracle steps whole periodic grids only")
@@ -44,6 +54,8 @@ def interpret(family, pallas_kwargs, *args, pow_flavour="pd"):
     if name == "threefry_bits":
         grid = pallas_kwargs["grid"]
         n = int(grid[0] if isinstance(grid, (tuple, list)) else grid)
+        if c["op"] == "pcg":
+            return oracle.pcg_hash(n)
         if c["op"] == "bits":
             return oracle.random_bits(args[0], n)
         if c["op"] == "uniform":

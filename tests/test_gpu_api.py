@@ -233,3 +233,38 @@ def test_chunked_adaptive_counts_are_exact():
     np.testing.assert_array_equal(state[pick, 0], want[1])
     np.testing.assert_array_equal(accepted[pick], want[5].astype(np.int32))
     np.testing.assert_array_equal(rejected[pick], want[4].astype(np.int32))
+
+
+# ------------------------------------------------------------------ device-resident stepping
+def test_stepper_keeps_the_grid_on_the_device():
+    # examples/04_reaction_diffusion.py:92-109: ping-pong buffers, one wait, device-side time
+    size = 128
+    u, v = W.gray_scott_initial_state(size, patches=4, patch=16)
+    call = H.gs_solver(size, size, math_mode=SAFE, steps=4)
+    stepper = pd.Stepper(call, u, v)
+    stepper.advance(5).advance(2)
+    got_u, got_v = stepper.read()
+    want = oracle.gray_scott(u, v, steps=28)
+    np.testing.assert_array_equal(got_u, want[0])
+    np.testing.assert_array_equal(got_v, want[1])
+    assert stepper.launches == 7 and stepper.gpu_time > 0.0
+
+
+def test_stepper_feeds_state_and_keeps_parameters():
+    n = 3000
+    args = W.lotka_volterra_ensemble(n)
+    stepper = pd.Stepper(H.lv_solver(n, steps=100, math_mode=SAFE), *args)
+    got = stepper.advance(3).read()
+    want = oracle.lv_rk4(*args, dt=0.01, steps=300)
+    np.testing.assert_array_equal(got[0], want[0])
+    np.testing.assert_array_equal(got[1], want[1])
+
+
+def test_stepper_rejects_mismatched_feedback():
+    n = 64
+    args = W.lotka_volterra_ensemble(n)
+    with pytest.raises(pd.DispatchError, match="one input slot per output"):
+        pd.Stepper(H.lv_solver(n, steps=1), *args, feedback=[0])
+    key = W.gbm_key(0)
+    with pytest.raises(pd.DispatchError, match="cannot feed"):
+        pd.Stepper(H.gbm_solver(32, steps=4), key)

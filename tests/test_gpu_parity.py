@@ -212,6 +212,38 @@ def test_gbm_path_offset_is_global_index():
     np.testing.assert_array_equal(part, whole[2048:3072])
 
 
+def test_pcg_hash_exact():
+    got = H.threefry_solver("pcg", 100_000)(W.gbm_key(0))
+    np.testing.assert_array_equal(got, oracle.pcg_hash(100_000))
+
+
+@pytest.mark.parametrize("mode,rtol", [(SAFE, 1e-5), (FAST, 1e-4)])
+def test_gbm_pcg_matches_oracle(mode, rtol):
+    cfg = dict(s0=100.0, strike=105.0, r=0.03, sigma=0.2, t=1.0, steps=256)
+    n = 1 << 14
+    got = H.gbm_pcg_solver(n, math_mode=mode, output="terminal", **cfg)()
+    want, _ = oracle.gbm_pcg(n, **cfg)
+    np.testing.assert_allclose(got, want, rtol=rtol)
+
+
+def test_gbm_pcg_black_scholes_and_offsets(interpret_provider):
+    # examples/03_sde_montecarlo.py:137-146 for the hand-written kernel
+    n = 1 << 20
+    call = H.gbm_pcg_solver(n, with_sums=True)
+    payoff, sums = call()
+    disc = np.exp(-0.03)
+    price = disc * sums[0] / n
+    stderr = disc * np.sqrt((sums[1] / n - (sums[0] / n) ** 2) / n)
+    assert abs(price - oracle.black_scholes_call(100.0, 105.0, 1.0, 0.03, 0.2)) < 5 * stderr
+    np.testing.assert_allclose(sums[0], payoff.astype(np.float64).sum(), rtol=1e-12)
+    part = H.gbm_pcg_solver(256, math_mode=SAFE, path_offset=4096)()
+    whole = H.gbm_pcg_solver(8192, math_mode=SAFE)()
+    np.testing.assert_array_equal(part, whole[4096:4352])
+    want = H.gbm_pcg_solver(512, math_mode=SAFE).interpret()
+    # payoff = S_T - K: rtol 1e-5 on S_T ~ 100 is 1e-3 absolute on the payoff
+    np.testing.assert_allclose(H.gbm_pcg_solver(512, math_mode=SAFE)(), want, rtol=1e-5, atol=2e-3)
+
+
 # ------------------------------------------------------------------ Gray-Scott
 @pytest.mark.parametrize("shape", [(32, 32), (30, 50), (64, 128), (96, 256), (33, 132), (256, 1024)])
 @pytest.mark.parametrize("steps", [1, 2, 7])

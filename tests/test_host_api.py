@@ -76,7 +76,9 @@ def test_explain_other_families():
     d = H.gs_solver(30, 50).explain(H.shaped(30, 50), H.shaped(30, 50))
     assert d.cuda_kernel == "pd_gs_cell_kernel"
     d = H.gbm_solver(1 << 16, with_sums=True).explain(H.shaped(2, dtype=np.uint32))
-    assert d.cuda_kernel == "pd_gbm_kernel" and d.launches == 2
+    assert d.cuda_kernel == "pd_gbm_kernel<threefry>" and d.launches == 2
+    d = H.gbm_pcg_solver(1 << 16).explain()
+    assert d.cuda_kernel == "pd_gbm_kernel<pcg>"
 
 
 def test_explain_logging_once_per_shape(monkeypatch, capsys):

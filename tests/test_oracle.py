@@ -199,6 +199,20 @@ def test_gbm_path_offset_selects_global_streams():
     np.testing.assert_array_equal(part, whole[128:192])
 
 
+def test_pcg_hash_restatements_agree_and_price_matches_black_scholes():
+    np.testing.assert_array_equal(oracle.pcg_hash(50_000), oracle_np.pcg_hash(np.arange(50_000)))
+    u = oracle_np.pcg_uniform01(np.arange(1 << 18))
+    assert 0.0 < u.min() and u.max() <= 1.0 and abs(u.mean() - 0.5) < 2e-3
+    cfg = dict(s0=100.0, strike=105.0, r=0.03, sigma=0.2, t=1.0, steps=256)  # examples/03_sde_montecarlo.py:30-32
+    _, payoff = oracle.gbm_pcg(1 << 16, **cfg)
+    disc = np.exp(-0.03)
+    price, stderr = disc * payoff.mean(), disc * payoff.std(ddof=1) / np.sqrt(payoff.size)
+    assert abs(price - oracle.black_scholes_call(100.0, 105.0, 1.0, 0.03, 0.2)) < 5 * stderr
+    part, _ = oracle.gbm_pcg(64, path_offset=1000, **cfg)
+    whole, _ = oracle.gbm_pcg(1064, **cfg)
+    np.testing.assert_array_equal(part, whole[1000:])
+
+
 # ------------------------------------------------------------------ Gray-Scott
 def test_gray_scott_fixture_and_numpy_agreement():
     g = load("gray_scott")
