@@ -56,6 +56,8 @@ def parse_args():
     ap.add_argument("--math-mode", default="fast", choices=["safe", "relaxed", "fast"])
     ap.add_argument("--no-families", action="store_true", help="skip the short per-family measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="set a native tuning knob (pd_set_tuning), e.g. --tune vdp_variant=0")
     return ap.parse_args()
 
 
@@ -202,6 +204,10 @@ def main():
 
     import palladium_b200 as pd
     from palladium_b200 import _native, families, pl, workloads as W
+
+    for item in args.tune:
+        key, _, val = item.partition("=")
+        _native.set_tuning(key, int(val))
 
     def barrier():
         if world > 1:

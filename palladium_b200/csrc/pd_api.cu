@@ -48,6 +48,7 @@ std::map<std::string, int64_t>& tuning() {
         {"lv_block", 0},             // 0 = choose from N
         {"vdp_variant", 1},          // 0 direct, 1 persistent warps with lane refill
         {"vdp_block", 128},
+        {"vdp_refill_every", 8},     // attempts between refill checks
         {"vdp_blocks_per_sm", 0},    // 0 = about 1024 resident threads per SM
         {"gbm_block", 256},
         {"gbm_blocks_per_sm", 0},
@@ -526,6 +527,8 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
                 if (p->out_layout == 0) a.real_out = (float*)out[5];
             }
             a.n = n; a.max_steps = (int)p->max_steps;
+            a.refill_every = (int)knob("vdp_refill_every");
+            if (a.refill_every < 1) a.refill_every = 1;
             a.t1 = (float)p->t1; a.rtol = (float)p->rtol; a.atol = (float)p->atol; a.dt0 = (float)p->dt0;
             a.safety = (float)p->safety; a.factor_min = (float)p->factor_min; a.factor_max = (float)p->factor_max;
             a.coeff1 = (float)((p->icoeff + p->pcoeff) / (double)p->error_order);

@@ -27,6 +27,7 @@ struct PdVdpArgs {
     unsigned long long* cursor;  // work-queue head (scratch, zeroed by the caller)
     int64_t n;
     int max_steps;
+    int refill_every;  // attempts between two refill checks of a warp
     float t1, rtol, atol, dt0, safety, factor_min, factor_max, coeff1, coeff2;
 };
 
