@@ -358,6 +358,15 @@ static inline df df_div(df a, df b) {
     float q3 = r.hi / b.hi;
     return df_add(quick_two_sum(q1, q2), dfc(q3));
 }
+/* 1 / b: q = 1 / b.hi, e = 1 - b q formed exactly, result q + q e */
+static inline df df_recip(df b) {
+    float q = 1.0f / b.hi;
+    df p = two_prod(b.hi, q);
+    p.lo = fmaf(b.lo, q, p.lo);
+    float e = (1.0f - p.hi) - p.lo;
+    return quick_two_sum(q, q * e);
+}
+static inline df df_twice(df a) { df r; r.hi = a.hi + a.hi; r.lo = a.lo + a.lo; return r; }
 static inline df df_sqrt(df a) {
     float s = sqrtf(a.hi);
     if (s == 0.0f) return dfc(0.0f);
@@ -375,6 +384,7 @@ ORC_API void orc_df_op(int op, int64_t n, const float* ah, const float* al, cons
             case 1: r = df_sub(a, b); break;
             case 2: r = df_mul(a, b); break;
             case 3: r = df_div(a, b); break;
+            case 5: r = df_recip(a); break;
             default: r = df_sqrt(a); break;
         }
         oh[i] = r.hi; ol[i] = r.lo;
@@ -425,7 +435,7 @@ ORC_API void orc_kepler_rk4_df32(int64_t n, const float* const* in, float* const
                                  int64_t steps) {
     const df dt = split_double(dt_), gm = split_double(gm_);
     df half_dt; half_dt.hi = 0.5f * dt.hi; half_dt.lo = 0.5f * dt.lo;
-    const df sixth_dt = df_div(dt, dfc(6.0f)), two = dfc(2.0f);
+    const df sixth_dt = df_div(dt, dfc(6.0f));
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; ++i) {
         df s[4];
@@ -437,7 +447,7 @@ ORC_API void orc_kepler_rk4_df32(int64_t n, const float* const* in, float* const
                 df r2 = df_add(df_mul(w[0], w[0]), df_mul(w[1], w[1]));
                 df r = df_sqrt(r2);
                 df r3 = df_mul(r2, r);
-                df g = df_div(gm, r3);
+                df g = df_mul(gm, df_recip(r3));
                 k[st][0] = w[2];
                 k[st][1] = w[3];
                 k[st][2] = df_neg(df_mul(w[0], g));
@@ -448,7 +458,7 @@ ORC_API void orc_kepler_rk4_df32(int64_t n, const float* const* in, float* const
                 }
             }
             for (int c = 0; c < 4; ++c) {
-                df sum = df_add(df_add(df_add(k[0][c], df_mul(two, k[1][c])), df_mul(two, k[2][c])), k[3][c]);
+                df sum = df_add(df_add(df_add(k[0][c], df_twice(k[1][c])), df_twice(k[2][c])), k[3][c]);
                 s[c] = df_add(s[c], df_mul(sixth_dt, sum));
             }
         }

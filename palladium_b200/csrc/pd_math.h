@@ -206,6 +206,20 @@ PD_HD pd_df32 pd_df_div(pd_df32 a, pd_df32 b) {
     return pd_df_add(q, pd_df_from_float(q3));
 }
 
+// 1 / b: one IEEE quotient digit q = 1 / b.hi, then one Newton step carried out
+// with error-free products: e = 1 - b q is formed exactly (b.hi q as a TwoProd,
+// 1 - p.hi exact by Sterbenz), and 1 / b = q (1 + e + O(e^2)), e ~ 2^-24.
+PD_HD pd_df32 pd_df_recip(pd_df32 b) {
+    const float q = pd_div(1.0f, b.hi);
+    pd_df32 p = pd_two_prod(b.hi, q);
+    p.lo = pd_fma(b.lo, q, p.lo);
+    const float e = pd_sub(pd_sub(1.0f, p.hi), p.lo);
+    return pd_fast_two_sum(q, pd_mul(q, e));
+}
+
+// 2 a, exact.
+PD_HD pd_df32 pd_df_twice(pd_df32 a) { return pd_df_make(pd_add(a.hi, a.hi), pd_add(a.lo, a.lo)); }
+
 // sqrt(df32): IEEE float sqrt as the seed, one Newton correction carried out
 // in df32:  r = s + (a - s*s) / (2 s).   a must be >= 0; sqrt(0) = 0.
 PD_HD pd_df32 pd_df_sqrt(pd_df32 a) {
