@@ -54,6 +54,7 @@ std::map<std::string, int64_t>& tuning() {
         {"gbm_blocks_per_sm", 0},
         {"gs_variant", -1},          // -1 = best for the shape; 0 per cell, 1 vec4 (one step), 2 temporal blocking
         {"gs_fuse", 4},              // steps fused per launch by variant 2 (2..4)
+        {"gs_persistent", 0},        // variant 2: one tile per block (0, faster at K = 4) or persistent blocks with cp.async prefetch (1)
         {"df32_block", 128},
         {"time_kernels", 0},
     };
@@ -319,9 +320,12 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 plan->grid[1] = (rows_alloc + PD_GS_TILE_ROWS - 1) / PD_GS_TILE_ROWS;
             } else {
                 const int k = p->steps < fuse ? (int)p->steps : fuse;
-                plan->variant = 10 + k;  // the kernel of the full-size launches
-                plan->kernel = mt->kernel_ptr(family, 10 + k);
-                plan->kernel_name = k == 4 ? "pd_gs_tb_kernel<4>" : k == 3 ? "pd_gs_tb_kernel<3>" : "pd_gs_tb_kernel<2>";
+                const bool persistent = knob("gs_persistent") != 0;
+                plan->variant = (persistent ? 20 : 10) + k;  // the kernel of the full-size launches
+                plan->kernel = mt->kernel_ptr(family, plan->variant);
+                plan->kernel_name = persistent
+                    ? (k == 4 ? "pd_gs_tbp_kernel<4>" : k == 3 ? "pd_gs_tbp_kernel<3>" : "pd_gs_tbp_kernel<2>")
+                    : (k == 4 ? "pd_gs_tb_kernel<4>" : k == 3 ? "pd_gs_tb_kernel<3>" : "pd_gs_tb_kernel<2>");
                 plan->items = 4;  // cells per thread per row
                 plan->block[0] = 256;
                 plan->grid[0] = (p->cols + 119) / 120;
@@ -587,7 +591,8 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             const float* src_v = (const float*)in[1];
             // Fused launches of k steps each (k = 1 for the one-step kernels); the
             // last launch must land in `out`, so an odd launch count starts there.
-            const int fuse = plan.variant >= 12 ? plan.variant - 10 : 1;
+            const int tb_base = plan.variant >= 22 ? 20 : 10;
+            const int fuse = plan.variant >= 12 ? plan.variant - tb_base : 1;
             bool to_out = (plan.launches % 2) == 1;
             int64_t done = 0;
             while (done < p->steps) {
@@ -597,7 +602,7 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
                 a.vo = to_out ? ping_v : pong_v;
                 if (p->halo == 0) { a.row_lo = 0; a.row_hi = rows_alloc; }
                 else { a.row_lo = (int)(done + k); a.row_hi = rows_alloc - (int)(done + k); }
-                const int variant = k >= 2 ? 10 + k : (plan.variant >= 12 ? 1 : plan.variant);
+                const int variant = k >= 2 ? tb_base + k : (plan.variant >= 12 ? 1 : plan.variant);
                 PD_CUDA_TRY(mt->gray_scott(a, variant, st));
                 src_u = a.uo; src_v = a.vo;
                 to_out = !to_out;

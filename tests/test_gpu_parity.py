@@ -258,10 +258,11 @@ def test_gray_scott_safe_bit_exact(shape, steps):
     np.testing.assert_array_equal(got_v, want_v)
 
 
+@pytest.mark.parametrize("persistent", [0, 1])
 @pytest.mark.parametrize("fuse", [2, 3, 4])
 @pytest.mark.parametrize("shape,steps", [((256, 1024), 9), ((96, 256), 4), ((33, 132), 5), ((40, 128), 7),
                                          ((64, 360), 8), ((31, 244), 3), ((5, 128), 6)])
-def test_gray_scott_temporal_blocking_bit_exact(shape, steps, fuse):
+def test_gray_scott_temporal_blocking_bit_exact(shape, steps, fuse, persistent):
     """K fused steps in shared memory equal K single steps: tiles that overhang
     the grid in both directions, periodic wrap through the halo, remainders."""
     from palladium_b200 import _native
@@ -271,12 +272,14 @@ def test_gray_scott_temporal_blocking_bit_exact(shape, steps, fuse):
     u = (1.0 - 0.5 * rng.random(shape)).astype(np.float32)
     v = (0.25 * rng.random(shape)).astype(np.float32)
     _native.set_tuning("gs_fuse", fuse)
+    _native.set_tuning("gs_persistent", persistent)
     try:
         call = H.gs_solver(rows, cols, math_mode=SAFE, steps=steps)
-        assert call.explain(u, v).cuda_kernel.startswith("pd_gs_tb_kernel")
+        assert call.explain(u, v).cuda_kernel.startswith("pd_gs_tbp_kernel" if persistent else "pd_gs_tb_kernel")
         got_u, got_v = call(u, v)
     finally:
         _native.set_tuning("gs_fuse", 4)
+        _native.set_tuning("gs_persistent", 0)
     want_u, want_v = oracle.gray_scott(u, v, steps=steps)
     np.testing.assert_array_equal(got_u, want_u)
     np.testing.assert_array_equal(got_v, want_v)
