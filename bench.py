@@ -77,7 +77,7 @@ class ClockSampler:
         0x80: "hw_power_brake_slowdown",
     }
 
-    def __init__(self, index: int, period_s: float = 0.05):
+    def __init__(self, index: int, period_s: float = 0.01):
         self.index, self.period = index, period_s
         self.samples: list[int] = []
         self.reasons: set[str] = set()
