@@ -304,13 +304,13 @@ def run(args, rank: int, local_rank: int, world: int, barrier, max_over_ranks) -
     elif name == "gray_scott":
         size = args.n or 8192
         rows_total = size * world if world > 1 else size
-        halo = 4
+        halo = 16
         lo, hi = sharded.partition(rows_total, world, rank)
         u = torch.rand((hi - lo, size), device="cuda") * 0.5 + 0.5
         v = torch.rand((hi - lo, size), device="cuda") * 0.25
         cfg = {k: v_ for k, v_ in W.GRAY_SCOTT_CONFIG.items() if k not in ("steps", "size", "seed")}
         slab = sharded.GrayScottSlab(u, v, rows_total, halo=halo, constants=cfg, math_mode=args.math_mode)
-        per_step = 40
+        per_step = 64
         for _ in range(warmup):
             slab.advance(per_step)
         barrier()

@@ -130,7 +130,7 @@ class FfiCallable:
         return self._call_host(args)
 
     # ---- torch CUDA tensors: stream-ordered, no synchronisation ----------------
-    def _call_torch(self, args):
+    def _call_torch(self, args, out=None):
         import torch
 
         np_dtype = {torch.float32: "float32", torch.int32: "int32", torch.uint32: "uint32",
@@ -140,15 +140,19 @@ class FfiCallable:
         torch_dtype = {"float32": torch.float32, "int32": torch.int32, "uint32": torch.uint32,
                        "float64": torch.float64}
         device = args[0].device if args else torch.device("cuda", torch.cuda.current_device())
-        outs = [torch.empty(info.array_shape, dtype=torch_dtype[info.dtype.name], device=device)
-                for info in spec.outputs]
+        if out is not None:
+            outs = list(out) if isinstance(out, (list, tuple)) else [out]
+        else:
+            outs = [torch.empty(info.array_shape, dtype=torch_dtype[info.dtype.name], device=device)
+                    for info in spec.outputs]
         bound.launch_device(list(args), outs)
         return outs[0] if len(outs) == 1 else tuple(outs)
 
-    def on_device(self, *args):
+    def on_device(self, *args, out=None):
         """Stream-ordered launch returning torch CUDA tensors, also for families
-        without inputs (where `__call__` cannot tell a device call from a host call)."""
-        return self._call_torch(args)
+        without inputs (where `__call__` cannot tell a device call from a host call).
+        `out`: preallocated contiguous output tensors (views are fine) to write into."""
+        return self._call_torch(args, out)
 
     # ---- host buffers: the XLA:CPU handler contract -----------------------------
     def _call_host(self, args):

@@ -34,10 +34,15 @@ def _worker(rank, world, port, out_dir):
         u0, v0 = W.gray_scott_initial_state(512, seed=11, patches=16, patch=32)
         u0, v0 = u0[:rows].copy(), v0[:rows].copy()
         lo, hi = sharded.partition(rows, world, rank)
-        slab = sharded.GrayScottSlab(torch.from_numpy(u0[lo:hi]).cuda(), torch.from_numpy(v0[lo:hi]).cuda(), rows,
-                                     halo=halo, constants=dict(oracle.GS_DEFAULTS), math_mode="safe")
-        slab.advance(steps)
-        u, v = slab.owned()
+        results = []
+        for overlap in (True, False):
+            slab = sharded.GrayScottSlab(torch.from_numpy(u0[lo:hi]).cuda(), torch.from_numpy(v0[lo:hi]).cuda(), rows,
+                                         halo=halo, constants=dict(oracle.GS_DEFAULTS), math_mode="safe",
+                                         overlap=overlap)
+            slab.advance(steps)
+            results.append(slab.owned())
+        assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+        u, v = results[0]
         cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=64)
         res = sharded.gbm_monte_carlo(W.gbm_key(0), 100_003, cfg, math_mode="safe")
         torch.cuda.synchronize()
