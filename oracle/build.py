@@ -21,7 +21,8 @@ HERE = Path(__file__).resolve().parent
 ORACLE_LIB = HERE / "liboracle.so"
 REF_DIR = HERE / "_ref"
 REF_LIB = REF_DIR / "libmslref.so"
-REFERENCE_ROOT = Path(os.environ.get("PALLADIUM_REFERENCE", "/root/reference"))
+# The reference checkout: PALLADIUM_REFERENCE, else a directory named "reference" beside this repository.
+REFERENCE_ROOT = Path(os.environ.get("PALLADIUM_REFERENCE", str(HERE.parent.parent / "reference")))
 GOLDEN_RK4 = REFERENCE_ROOT / "tests" / "golden" / "rk4_lotka_volterra.metal"
 
 CFLAGS = ["-O2", "-ffp-contract=off", "-fno-fast-math", "-mfma", "-fopenmp", "-fPIC", "-shared",
