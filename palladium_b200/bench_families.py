@@ -7,8 +7,9 @@ dict that `bench.py` embeds in its JSON line under "families".
 (`bench.py --workload vdp_bs32|gbm|gray_scott|kepler_df32`), one rank per GPU.
 
 Algorithmic costs used for the roofline fractions:
-  adaptive BS3(2): one attempt = 97 float operations + 2 pow + 3 divisions
-      (counted from the kernel body; stall iterations are not attempts);
+  adaptive BS3(2): one attempt = 97 float operations + one log2, two exp2 and
+      three divisions, which are not counted (from the kernel body; stall
+      iterations are not attempts);
   GBM: one path-step = 4 Threefry-2x32-20 blocks = 4 x (20 rounds x 3 + 5 x 3 + 2)
       = 308 32-bit integer operations as written in the specification, plus
       log, sqrt, cos, exp;

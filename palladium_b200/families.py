@@ -10,7 +10,7 @@ that the `grid` / `in_specs` / `out_specs` / `out_shape` of the call describe
 the launch that family performs -- the same keywords, with the same meaning, a
 user of the reference already writes for `metal_call`.
 
-`trace(call_kwargs, family, *args)` produces the `KernelSpec` analogue: name,
+`trace(family, call_kwargs, *args)` produces the `KernelSpec` analogue: name,
 grid, and one `BlockInfo` per operand.
 """
 
