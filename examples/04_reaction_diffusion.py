@@ -1,0 +1,47 @@
+"""Method-of-lines PDE (the reference's examples/04_reaction_diffusion.py):
+Gray-Scott reaction-diffusion with explicit Euler on a periodic grid.  The grid
+stays on the device across all launches (`Stepper`); each launch advances four
+steps inside shared memory."""
+
+import sys
+from pathlib import Path
+
+import numpy as np
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))  # run from a source checkout
+
+import palladium_b200 as pd  # noqa: E402
+from palladium_b200 import families, pl  # noqa: E402
+
+SIZE = 512
+STEPS = 2000
+PER_LAUNCH = 4
+
+
+def initial_state(size, seed=11):
+    rng = np.random.default_rng(seed)
+    u = np.ones((size, size), np.float32)
+    v = np.zeros((size, size), np.float32)
+    m = size // 2
+    u[m - 8:m + 8, m - 8:m + 8] = 0.5
+    v[m - 8:m + 8, m - 8:m + 8] = 0.25
+    u += 0.02 * rng.standard_normal((size, size)).astype(np.float32)
+    return u, v
+
+
+def main():
+    full = pl.BlockSpec((SIZE, SIZE), lambda i, j: (0, 0))
+    shape = pl.ShapeDtypeStruct((SIZE, SIZE), np.float32)
+    call = pd.cuda_call(families.gray_scott(steps=PER_LAUNCH), grid=(SIZE, SIZE), in_specs=[full, full],
+                        out_specs=(full, full), out_shape=(shape, shape))
+    u0, v0 = initial_state(SIZE)
+    print(call.explain(u0, v0))
+    stepper = pd.Stepper(call, u0, v0)
+    stepper.advance(STEPS // PER_LAUNCH)
+    u, v = stepper.read()
+    print(f"Gray-Scott {SIZE}x{SIZE}, {STEPS} Euler steps: {stepper.gpu_time * 1e3:.2f} ms on the device "
+          f"({stepper.launches} launches), pattern energy {float(v.sum()):.1f}")
+
+
+if __name__ == "__main__":
+    main()

@@ -268,3 +268,14 @@ def test_stepper_rejects_mismatched_feedback():
     key = W.gbm_key(0)
     with pytest.raises(pd.DispatchError, match="cannot feed"):
         pd.Stepper(H.gbm_solver(32, steps=4), key)
+
+
+# ------------------------------------------------------------------ the example scripts run
+@pytest.mark.parametrize("script", ["01_ode_ensembles", "02_adaptive_lockstep", "03_sde_montecarlo",
+                                    "04_reaction_diffusion", "05_df32_precision"])
+def test_example_scripts_run(script):
+    import runpy
+    from pathlib import Path
+
+    path = Path(__file__).resolve().parent.parent / "examples" / f"{script}.py"
+    runpy.run_path(str(path), run_name="__main__")
