@@ -250,6 +250,21 @@ def test_stepper_keeps_the_grid_on_the_device():
     assert stepper.launches == 7 and stepper.gpu_time > 0.0
 
 
+def test_stepper_graph_replay_equals_eager_stepping():
+    size = 128
+    u, v = W.gray_scott_initial_state(size, patches=4, patch=16)
+    call = H.gs_solver(size, size, math_mode=SAFE, steps=2)
+    eager = pd.Stepper(call, u, v).advance(25).read()
+    graphed = pd.Stepper(call, u, v)
+    graphed.advance(11, graph=True).advance(14, graph=True)   # odd and even counts, graph reused
+    got = graphed.read()
+    assert graphed.launches == 25
+    np.testing.assert_array_equal(got[0], eager[0])
+    np.testing.assert_array_equal(got[1], eager[1])
+    want = oracle.gray_scott(u, v, steps=50)
+    np.testing.assert_array_equal(got[0], want[0])
+
+
 def test_stepper_feeds_state_and_keeps_parameters():
     n = 3000
     args = W.lotka_volterra_ensemble(n)
