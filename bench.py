@@ -156,6 +156,50 @@ def cpu_rk4(n_sample: int, threads: int | None = None):
     return rate, kind, cores, f"{n_sample} trajectories x {LV_STEPS} steps of the same ensemble, one pass, {dt:.2f} s"
 
 
+def cpu_family_baselines() -> dict:
+    """The CPU oracle (the port of each reference kernel) timed on all host cores
+    on a bounded sample of each family's workload: the reported CPU baseline of
+    the families other than the headline one."""
+    import oracle
+    from palladium_b200 import workloads as W
+
+    cores = len(os.sched_getaffinity(0))
+    oracle.set_threads(cores)
+    out = {"cores": cores, "kind": "port"}
+
+    def timed(fn):
+        t0 = time.perf_counter()
+        res = fn()
+        return time.perf_counter() - t0, res
+
+    n = 4096
+    x0, v0, mu = W.van_der_pol_ensemble(n)
+    cfg = {k: v for k, v in W.VDP_CONFIG.items() if k not in ("n", "seed")}
+    sec, res = timed(lambda: oracle.vdp_bs32(x0, v0, mu, pow="libm", **cfg))
+    attempts = float((res[4] + res[5]).sum())
+    out["vdp_bs32"] = {"sample": f"{n} trajectories, full {cfg['max_steps']}-iteration loop as the reference runs it",
+                       "seconds": sec, "attempts_per_s": attempts / sec,
+                       "loop_iterations_per_s": n * cfg["max_steps"] / sec}
+    n = 1 << 17
+    gcfg = {k: v for k, v in W.GBM_CONFIG.items() if k not in ("n", "seed")}
+    sec, _ = timed(lambda: oracle.gbm(W.gbm_key(0), n, **gcfg))
+    out["gbm"] = {"sample": f"{n} paths x {gcfg['steps']} steps", "seconds": sec,
+                  "path_steps_per_s": n * gcfg["steps"] / sec}
+    size, steps = 2048, 20
+    u = (np.random.default_rng(0).random((size, size)) * 0.5 + 0.5).astype(np.float32)
+    v = (np.random.default_rng(1).random((size, size)) * 0.25).astype(np.float32)
+    sec, _ = timed(lambda: oracle.gray_scott(u, v, steps=steps))
+    out["gray_scott"] = {"sample": f"{size} x {size}, {steps} steps", "seconds": sec,
+                         "cell_steps_per_s": size * size * steps / sec}
+    n, steps = 8192, 500
+    _, pairs = W.kepler_ensemble(n)
+    sec, _ = timed(lambda: oracle.kepler_rk4_df32(pairs, dt=1e-3, steps=steps))
+    out["kepler_df32"] = {"sample": f"{n} orbits x {steps} steps", "seconds": sec,
+                          "trajectory_steps_per_s": n * steps / sec}
+    return out
+
+
+
 def run_reference_arm(args):
     rank, _, world = dist_env()
     if rank != 0:
@@ -325,6 +369,8 @@ def main():
                 from palladium_b200 import bench_families
 
                 fam = bench_families.quick_summary()
+                if not args.no_cpu:
+                    fam["cpu_baselines"] = cpu_family_baselines()
             except Exception as exc:  # the headline line must still be printed
                 fam = {"error": f"{type(exc).__name__}: {exc}"}
 
