@@ -56,6 +56,7 @@ std::map<std::string, int64_t>& tuning() {
         {"gs_fuse", 4},              // steps fused per launch by variant 2 (2..4)
         {"gs_persistent", 0},        // variant 2: one tile per block (0, faster at K = 4) or persistent blocks with cp.async prefetch (1)
         {"df32_block", 128},
+        {"host_chunks", 32},         // chunks a large host-buffer call is cut into
         {"time_kernels", 0},
     };
     return t;
@@ -761,7 +762,9 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
         }
     }
     if (chunked) {
-        int64_t chunk = ((n + 11) / 12 + 4095) / 4096 * 4096;  // ~12 chunks, 16 KiB-aligned slices
+        int64_t want_chunks = knob("host_chunks");
+        if (want_chunks < 1) want_chunks = 1;
+        int64_t chunk = ((n + want_chunks - 1) / want_chunks + 4095) / 4096 * 4096;  // 16 KiB-aligned slices
         if (chunk < ((int64_t)1 << 16)) chunk = (int64_t)1 << 16;
         bool any_broadcast = false;
         for (int i = 0; i < n_in; ++i) {
