@@ -28,7 +28,7 @@ from collections.abc import Callable
 
 import numpy as np
 
-__all__ = ["partition", "GbmResult", "gbm_monte_carlo", "GrayScottSlab"]
+__all__ = ["partition", "ensemble_indices", "run_ensemble", "GbmResult", "gbm_monte_carlo", "GrayScottSlab"]
 
 
 def partition(n: int, world: int, rank: int) -> tuple[int, int]:
@@ -51,6 +51,65 @@ def _world(group=None) -> tuple[int, int]:
     if dist.is_available() and dist.is_initialized():
         return dist.get_rank(group), dist.get_world_size(group)
     return 0, 1
+
+
+# ----------------------------------------------------------------------------- ODE ensembles
+def ensemble_indices(n: int, world: int, rank: int, interleave: bool = False):
+    """The trajectories rank `rank` integrates: the contiguous slab of
+    `partition`, or every `world`-th trajectory starting at `rank` when
+    `interleave` is set.  Interleaving evens out the cost per rank when the cost
+    of a trajectory varies along the array (an adaptive solver over stiffness
+    parameters stored in sorted order)."""
+    if interleave:
+        if world <= 0 or not 0 <= rank < world:
+            raise ValueError(f"rank {rank} is not in a world of {world}")
+        return slice(rank, int(n), world)
+    lo, hi = partition(n, world, rank)
+    return slice(lo, hi)
+
+
+def run_ensemble(make_call: Callable, arrays, *, interleave: bool = False, gather: bool = False, group=None):
+    """Integrate this rank's share of a per-trajectory ensemble.
+
+    `arrays` are the full-length inputs (NumPy arrays or torch tensors, first
+    axis = trajectory), identical on every rank; `make_call(n_local)` returns the
+    call for `n_local` trajectories (a `cuda_call` / `cuda_call_jit` object, or any
+    function of the local arrays when the host logic runs on CPU ranks).
+    Trajectories are independent, so no data-path collective is needed; with
+    `gather=True` the outputs of all ranks are all-gathered and put back in
+    the original trajectory order, otherwise each rank returns its own share.
+    Returns (outputs tuple, index slice of this rank's trajectories)."""
+    import torch
+
+    rank, world = _world(group)
+    n = int(arrays[0].shape[0])
+    idx = ensemble_indices(n, world, rank, interleave)
+    local = []
+    for a in arrays:
+        part = a[idx]
+        local.append(part.contiguous() if isinstance(part, torch.Tensor) else np.ascontiguousarray(part))
+    n_local = int(local[0].shape[0])
+    outs = make_call(n_local)(*local)
+    outs = tuple(outs) if isinstance(outs, (tuple, list)) else (outs,)
+    if not gather or world == 1:
+        return outs, idx
+    dist = _dist()
+    cap = -(-n // world)              # the largest share; shorter shares are padded for the collective
+    full = []
+    for o in outs:
+        was_numpy = not isinstance(o, torch.Tensor)
+        t = torch.from_numpy(np.ascontiguousarray(o)) if was_numpy else o
+        pad = torch.zeros((cap, *t.shape[1:]), dtype=t.dtype, device=t.device)
+        pad[:n_local] = t
+        parts = [torch.empty_like(pad) for _ in range(world)]
+        dist.all_gather(parts, pad, group=group)
+        whole = torch.empty((n, *t.shape[1:]), dtype=t.dtype, device=t.device)
+        for r, part in enumerate(parts):
+            ridx = ensemble_indices(n, world, r, interleave)
+            count = len(range(*ridx.indices(n)))
+            whole[ridx] = part[:count]
+        full.append(whole.numpy() if was_numpy else whole)
+    return tuple(full), idx
 
 
 # ----------------------------------------------------------------------------- Monte Carlo

@@ -19,6 +19,15 @@ def _free_port():
         return s.getsockname()[1]
 
 
+VDP_CFG = dict(t1=2.0, rtol=1e-5, atol=1e-7, dt0=0.01, max_steps=3000)
+N_VDP = 20_011
+
+
+def _sorted_vdp(n):
+    x0, v0, mu = W.van_der_pol_ensemble(n)
+    return x0, v0, np.sort(mu)
+
+
 def _worker(rank, world, port, out_dir):
     import torch
     import torch.distributed as dist
@@ -45,9 +54,27 @@ def _worker(rank, world, port, out_dir):
         u, v = results[0]
         cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=64)
         res = sharded.gbm_monte_carlo(W.gbm_key(0), 100_003, cfg, math_mode="safe")
+        # adaptive ensemble with the stiffness sorted along the array: interleaved shares,
+        # outputs all-gathered on the device and put back in trajectory order
+        import palladium_b200 as pd
+        from palladium_b200 import families, pl
+
+        def make(n_local):
+            sh = pl.ShapeDtypeStruct((n_local,), np.float32)
+            return pd.cuda_call_jit(families.vdp_bs32(**VDP_CFG), grid=(n_local,), out_shape=(sh,) * 6,
+                                    math_mode="safe")
+
+        ins = [torch.from_numpy(a).cuda() for a in _sorted_vdp(N_VDP)]
+        ens = {}
+        for interleave in (False, True):
+            outs, _ = sharded.run_ensemble(make, ins, interleave=interleave, gather=True)
+            ens[interleave] = [o.cpu().numpy() for o in outs]
+        for a, b in zip(ens[False], ens[True]):
+            np.testing.assert_array_equal(a, b)
         torch.cuda.synchronize()
         np.savez(os.path.join(out_dir, f"r{rank}.npz"), u=u.cpu().numpy(), v=v.cpu().numpy(), lo=lo, hi=hi,
-                 price=res.price, sums=np.array(res.sums), out=res.local_output.cpu().numpy(), plo=res.local_lo)
+                 price=res.price, sums=np.array(res.sums), out=res.local_output.cpu().numpy(), plo=res.local_lo,
+                 **{f"vdp{i}": a for i, a in enumerate(ens[True])})
     finally:
         dist.destroy_process_group()
 
@@ -66,6 +93,7 @@ def test_two_gpus_halo_exchange_and_all_reduce(tmp_path):
     cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=64)
     terminal, payoff = oracle.gbm(W.gbm_key(0), 100_003, **cfg)
     p64 = payoff.astype(np.float64)
+    want_vdp = oracle.vdp_bs32(*_sorted_vdp(N_VDP), pow="pd", **VDP_CFG)
     outs = []
     for rank in range(world):
         part = np.load(tmp_path / f"r{rank}.npz")
@@ -74,4 +102,6 @@ def test_two_gpus_halo_exchange_and_all_reduce(tmp_path):
         np.testing.assert_array_equal(part["v"], want_v[lo:hi])
         np.testing.assert_allclose(part["sums"][0], p64.sum(), rtol=1e-5)
         outs.append(part["out"])
+        for i, want in enumerate(want_vdp):
+            np.testing.assert_array_equal(part[f"vdp{i}"], want)
     np.testing.assert_allclose(np.concatenate(outs), terminal, rtol=1e-5)

@@ -63,6 +63,15 @@ def _worker(rank, world, port, case, out_dir):
             u, v = slab.owned()
             np.savez(os.path.join(out_dir, f"gs_{rank}.npz"), u=u.numpy(), v=v.numpy(), lo=lo, hi=hi,
                      exchanges=slab.exchanges)
+        elif case.startswith("ensemble"):
+            n = 1001
+            ins = W.lotka_volterra_ensemble(n)
+            make = lambda n_local: (lambda *a: oracle.lv_rk4(*a, dt=0.01, steps=20))
+            interleave = case.endswith("interleave")
+            (x, y), idx = sharded.run_ensemble(make, ins, interleave=interleave, gather=True)
+            (lx, ly), _ = sharded.run_ensemble(make, ins, interleave=interleave)
+            np.savez(os.path.join(out_dir, f"ens_{rank}.npz"), x=x, y=y, lx=lx, ly=ly,
+                     idx=np.arange(n)[idx])
         elif case == "gbm":
             cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=32)
             res = sharded.gbm_monte_carlo(W.gbm_key(0), 1001, cfg, path_fn=_oracle_paths)
@@ -88,6 +97,31 @@ def test_gray_scott_slabs_with_halo_exchange_equal_the_periodic_grid(world, tmp_
         np.testing.assert_array_equal(part["u"], want_u[lo:hi])
         np.testing.assert_array_equal(part["v"], want_v[lo:hi])
         assert int(part["exchanges"]) == 4  # ceil(11 / 3)
+
+
+@pytest.mark.parametrize("world,case", [(2, "ensemble"), (3, "ensemble_interleave")])
+def test_ensemble_shares_and_gather_restore_trajectory_order(world, case, tmp_path):
+    _run(world, case, tmp_path)
+    n = 1001
+    want_x, want_y = oracle.lv_rk4(*W.lotka_volterra_ensemble(n), dt=0.01, steps=20)
+    seen = []
+    for rank in range(world):
+        part = np.load(tmp_path / f"ens_{rank}.npz")
+        np.testing.assert_array_equal(part["x"], want_x)      # gathered: whole ensemble, original order
+        np.testing.assert_array_equal(part["y"], want_y)
+        np.testing.assert_array_equal(part["lx"], want_x[part["idx"]])   # local share only
+        np.testing.assert_array_equal(part["ly"], want_y[part["idx"]])
+        seen.append(part["idx"])
+    assert sorted(np.concatenate(seen).tolist()) == list(range(n))
+    if case.endswith("interleave"):
+        assert seen[1][:3].tolist() == [1, 1 + world, 1 + 2 * world]
+
+
+def test_ensemble_indices():
+    assert sharded.ensemble_indices(10, 2, 1) == slice(5, 10)
+    assert sharded.ensemble_indices(10, 3, 2, interleave=True) == slice(2, 10, 3)
+    with pytest.raises(ValueError):
+        sharded.ensemble_indices(10, 2, 2, interleave=True)
 
 
 def test_gray_scott_single_rank_wraps_its_own_halo():
