@@ -60,7 +60,9 @@ typedef enum pd_family {
     PD_FAMILY_KEPLER_RK4_DF32 = 5, /* same df32 RK4 scheme on the two-body problem */
     PD_FAMILY_THREEFRY_BITS = 6, /* random_bits / uniform / fold_in, src/palladium/emit/rules.py:168-201 */
     PD_FAMILY_GBM_PCG = 7,       /* gbm_paths with pcg_hash, the hand-written kernel GBM_MSL, examples/03_sde_montecarlo.py:34-70 */
-    PD_FAMILY_COUNT = 8
+    PD_FAMILY_CUSTOM_ODE = 8,    /* a caller-supplied right-hand side, compiled at run time: the counterpart of
+                                    handing the handler MSL source + entry-point name, native/ffi/palladium_ffi.cpp:136-148 */
+    PD_FAMILY_COUNT = 9
 } pd_family;
 
 /* ---- per-family parameter blocks (passed by pointer + sizeof) ------------ */
@@ -136,6 +138,39 @@ typedef struct pd_threefry_params {
     int64_t count;
 } pd_threefry_params;
 
+/* An ensemble of independent ODE systems y' = f(t, y, p) whose right-hand side
+ * the caller writes as CUDA C statements, the body of
+ *     void rhs(float t, const float* y, const float* p, float* dy)
+ * (y and dy have `dim` elements, p has `nparam`; pd_math.h's helpers, e.g.
+ * pd_powf and the df32 operations, are in scope).  The library wraps it in an
+ * integrator loop, compiles the text with NVRTC under the flag set of the math
+ * mode (first use of a source text; cached for the process, as the reference
+ * caches compiled pipelines by source text, palladium_ffi.cpp:44-49,75-84) and
+ * launches one thread per system.
+ *   method PD_ODE_RK4:  classic RK4, `steps` steps of `dt`; the arithmetic order
+ *     of the Lotka-Volterra family (stage y + f32(dt/2)*k, combine
+ *     ((k1 + 2 k2) + 2 k3) + k4, times f32(dt/6)).
+ *     in: dim state arrays then nparam parameter arrays, (N) f32.  out: dim arrays.
+ *   method PD_ODE_BS32: Bogacki-Shampine 3(2) with the PI controller, counters
+ *     and stall semantics of the Van der Pol family.
+ *     in: as above.  out: t, dim state arrays, steps, rejected, real, (N) f32.
+ * Compiler errors in the right-hand side come back as PD_ERR_INVALID_ARGUMENT
+ * with the compiler's log in `err`. */
+#define PD_ODE_RK4 0
+#define PD_ODE_BS32 1
+#define PD_ODE_MAX_DIM 8
+#define PD_ODE_MAX_PARAM 8
+typedef struct pd_custom_ode_params {
+    const char* rhs_source;   /* NUL-terminated; must stay valid for the call only */
+    int64_t dim, nparam, method;
+    double dt;                /* RK4 */
+    int64_t steps;
+    double t1, rtol, atol, dt0;   /* BS3(2) */
+    double pcoeff, icoeff, safety, factor_min, factor_max;
+    int64_t error_order;
+    int64_t max_steps;
+} pd_custom_ode_params;
+
 /* ---- launch geometry report (the `.explain()` payload) -------------------- */
 typedef struct pd_launch_info {
     char kernel_name[64];
@@ -149,6 +184,13 @@ typedef struct pd_launch_info {
     int32_t dynamic_smem_bytes;
     int32_t blocks_per_sm;     /* occupancy; -1 when no CUDA device is present */
 } pd_launch_info;
+
+/* Compile a PD_FAMILY_CUSTOM_ODE right-hand side for sm_100a without loading or
+ * launching it: needs NVRTC but no CUDA device, so a host can reject a faulty
+ * right-hand side where it is defined (the reference raises at trace time,
+ * before any dispatch).  `log` receives the compiler's messages. */
+PD_API int pd_custom_ode_check(const pd_custom_ode_params* params, size_t params_bytes, int math_mode,
+                               char* log, size_t log_cap, char* err, size_t err_cap);
 
 /* ABI version of the loaded library (== PD_ABI_VERSION it was built with). */
 PD_API int pd_version(void);

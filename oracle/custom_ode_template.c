@@ -1,0 +1,113 @@
+/* CPU oracle for run-time right-hand sides.  TEST INFRASTRUCTURE ONLY.
+ *
+ * oracle/custom_ode.py pastes a right-hand side (the same text the CUDA
+ * library compiles with NVRTC) at the marker below and builds this file with
+ * gcc -O2 -ffp-contract=off, so every float operation rounds once, in source
+ * order.  The two loops restate, for a state of ORC_DIM components:
+ *   - the fixed-step RK4 loop of the reference's ensemble kernel
+ *     (examples/01_ode_ensembles.py:72-91; operation order of
+ *     tests/golden/rk4_lotka_volterra.metal:90-94,186,234-258);
+ *   - the adaptive Bogacki-Shampine 3(2) loop with PI controller of
+ *     examples/02_adaptive_lockstep.py:69-171, run for the full max_steps
+ *     iterations as the reference runs it (no early exit here).
+ * Parity unpinned: the reference holds no numeric vectors for either loop on
+ * systems other than its own examples.
+ */
+#include <stdint.h>
+#include <math.h>
+#include "pd_math.h"
+
+#ifndef ORC_NPARAM_ALLOC
+#define ORC_NPARAM_ALLOC 1
+#endif
+
+static inline void user_rhs(float t, const float* y, const float* p, float* dy) {
+    (void)t; (void)p;
+/*ORC_RHS*/
+}
+
+__attribute__((visibility("default")))
+void orc_custom_rk4(int64_t n, const float* const* in, float* const* out, int64_t steps, double dt) {
+    const float hh = (float)(0.5 * dt), hf = (float)dt, h6 = (float)(dt / 6.0);
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        float y[ORC_DIM], p[ORC_NPARAM_ALLOC], w[ORC_DIM], k1[ORC_DIM], k2[ORC_DIM], k3[ORC_DIM], k4[ORC_DIM];
+        for (int c = 0; c < ORC_DIM; ++c) y[c] = in[c][i];
+        for (int c = 0; c < ORC_NPARAM; ++c) p[c] = in[ORC_DIM + c][i];
+        for (int64_t s = 0; s < steps; ++s) {
+            const float t = (float)s * hf;
+            user_rhs(t, y, p, k1);
+            for (int c = 0; c < ORC_DIM; ++c) w[c] = y[c] + hh * k1[c];
+            user_rhs(t + hh, w, p, k2);
+            for (int c = 0; c < ORC_DIM; ++c) w[c] = y[c] + hh * k2[c];
+            user_rhs(t + hh, w, p, k3);
+            for (int c = 0; c < ORC_DIM; ++c) w[c] = y[c] + hf * k3[c];
+            user_rhs(t + hf, w, p, k4);
+            for (int c = 0; c < ORC_DIM; ++c)
+                y[c] = y[c] + h6 * (((k1[c] + 2.0f * k2[c]) + 2.0f * k3[c]) + k4[c]);
+        }
+        for (int c = 0; c < ORC_DIM; ++c) out[c][i] = y[c];
+    }
+}
+
+static inline float max_nan(float a, float b) { return (a != a) ? a : (b != b) ? b : (a > b ? a : b); }
+static inline float min_nan(float a, float b) { return (a != a) ? a : (b != b) ? b : (a < b ? a : b); }
+
+/* out: t, ORC_DIM states, steps, rejected, real.  pow_flavour 0: libm powf; 1: pd_powf. */
+__attribute__((visibility("default")))
+void orc_custom_bs32(int64_t n, const float* const* in, float* const* out, double t1_, double rtol_, double atol_,
+                     double dt0_, double pcoeff, double icoeff, double safety_, double fmin_, double fmax_,
+                     int64_t error_order, int64_t max_steps, int pow_flavour) {
+    const float T1 = (float)t1_, RTOL = (float)rtol_, ATOL = (float)atol_, DT0 = (float)dt0_;
+    const float SAFETY = (float)safety_, FMIN = (float)fmin_, FMAX = (float)fmax_;
+    const float coeff1 = (float)((icoeff + pcoeff) / (double)error_order);
+    const float coeff2 = (float)(-pcoeff / (double)error_order);
+    const float c29 = (float)(2.0 / 9.0), c13 = (float)(1.0 / 3.0), c49 = (float)(4.0 / 9.0);
+    const float c724 = (float)(7.0 / 24.0), c14 = (float)(1.0 / 4.0), c18 = (float)(1.0 / 8.0);
+#pragma omp parallel for schedule(dynamic, 4)
+    for (int64_t i = 0; i < n; ++i) {
+        float y[ORC_DIM], p[ORC_NPARAM_ALLOC], k1[ORC_DIM], k2[ORC_DIM], k3[ORC_DIM], k4[ORC_DIM], w[ORC_DIM],
+            y3[ORC_DIM];
+        for (int c = 0; c < ORC_DIM; ++c) y[c] = in[c][i];
+        for (int c = 0; c < ORC_NPARAM; ++c) p[c] = in[ORC_DIM + c][i];
+        float t = 0.0f, dt = DT0, prev_inv_err = 1.0f, steps = 0.0f, rejected = 0.0f, real = 0.0f;
+        user_rhs(t, y, p, k1);
+        for (int64_t it = 0; it < max_steps; ++it) {
+            const int was_real = t < T1;
+            dt = min_nan(dt, T1 - t);
+            for (int c = 0; c < ORC_DIM; ++c) w[c] = y[c] + (0.5f * dt) * k1[c];
+            user_rhs(t + 0.5f * dt, w, p, k2);
+            for (int c = 0; c < ORC_DIM; ++c) w[c] = y[c] + (0.75f * dt) * k2[c];
+            user_rhs(t + 0.75f * dt, w, p, k3);
+            for (int c = 0; c < ORC_DIM; ++c) y3[c] = y[c] + dt * ((c29 * k1[c] + c13 * k2[c]) + c49 * k3[c]);
+            user_rhs(t + dt, y3, p, k4);
+            float err_norm = 0.0f;
+            for (int c = 0; c < ORC_DIM; ++c) {
+                const float y2 = y[c] + dt * (((c724 * k1[c] + c14 * k2[c]) + c13 * k3[c]) + c18 * k4[c]);
+                const float ratio = fabsf(y3[c] - y2) / (ATOL + RTOL * fabsf(y3[c]));
+                err_norm = c == 0 ? ratio : max_nan(err_norm, ratio);
+            }
+            const int accept = err_norm <= 1.0f;
+            if (accept) {
+                t = t + dt;
+                for (int c = 0; c < ORC_DIM; ++c) { y[c] = y3[c]; k1[c] = k4[c]; }
+            }
+            err_norm = max_nan(err_norm, 1e-9f);
+            const float inv_err = 1.0f / err_norm;
+            float pa, pb;
+            if (pow_flavour == 1) { pa = pd_powf(inv_err, coeff1); pb = pd_powf(prev_inv_err, coeff2); }
+            else { pa = powf(inv_err, coeff1); pb = powf(prev_inv_err, coeff2); }
+            const float factor = (SAFETY * pa) * pb;
+            if (accept) prev_inv_err = inv_err;
+            dt = dt * min_nan(max_nan(factor, FMIN), FMAX);
+            steps = steps + (accept ? 1.0f : 0.0f);
+            rejected = rejected + (accept ? 0.0f : 1.0f);
+            real = real + ((was_real && accept) ? 1.0f : 0.0f);
+        }
+        out[0][i] = t;
+        for (int c = 0; c < ORC_DIM; ++c) out[1 + c][i] = y[c];
+        out[ORC_DIM + 1][i] = steps;
+        out[ORC_DIM + 2][i] = rejected;
+        out[ORC_DIM + 3][i] = real;
+    }
+}

@@ -49,6 +49,7 @@ EXPORTED_SYMBOLS = (
     "pd_measure_int32_alu_peak",
     "pd_last_kernel_ms",
     "pd_gray_scott_static",
+    "pd_custom_ode_check",
 )
 
 FAMILY_IDS = {
@@ -60,6 +61,7 @@ FAMILY_IDS = {
     "kepler_rk4_df32": 5,
     "threefry_bits": 6,
     "gbm_pcg": 7,
+    "custom_ode": 8,
 }
 
 _i64 = ctypes.c_int64
@@ -96,6 +98,13 @@ class KeplerRk4Df32Params(ctypes.Structure):
 
 class ThreefryParams(ctypes.Structure):
     _fields_ = [("op", _i64), ("count", _i64)]
+
+
+class CustomOdeParams(ctypes.Structure):
+    _fields_ = [("rhs_source", ctypes.c_char_p), ("dim", _i64), ("nparam", _i64), ("method", _i64), ("dt", _dbl),
+                ("steps", _i64), ("t1", _dbl), ("rtol", _dbl), ("atol", _dbl), ("dt0", _dbl), ("pcoeff", _dbl),
+                ("icoeff", _dbl), ("safety", _dbl), ("factor_min", _dbl), ("factor_max", _dbl),
+                ("error_order", _i64), ("max_steps", _i64)]
 
 
 class LaunchInfo(ctypes.Structure):
@@ -144,6 +153,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pd_last_kernel_ms.argtypes = []
     lib.pd_gray_scott_static.restype = ci
     lib.pd_gray_scott_static.argtypes = [ctypes.POINTER(GrayScottParams), ci, vp, vp, vp, vp, vp, cp, sz]
+    lib.pd_custom_ode_check.restype = ci
+    lib.pd_custom_ode_check.argtypes = [ctypes.POINTER(CustomOdeParams), sz, ci, cp, sz, cp, sz]
 
 
 def library() -> ctypes.CDLL:
@@ -171,12 +182,14 @@ def library() -> ctypes.CDLL:
     return _lib
 
 
-_ERR_CAP = 1024
+_ERR_CAP = 4096
 
 
 def _raise(code: int, message: bytes) -> None:
     text = message.decode("utf-8", "replace") or f"native call failed with status {code}"
     if code == 1:
+        if "does not compile" in text:
+            raise EmitError(text)
         raise DispatchError(text)
     if code == 3:
         raise DispatchError(text) if "no CUDA device" in text else PalladiumError(text)
@@ -289,3 +302,15 @@ def gray_scott_static(params: GrayScottParams, math_mode: int, u: int, v: int, u
     rc = library().pd_gray_scott_static(ctypes.byref(params), math_mode, u, v, uo, vo, stream or None, err, _ERR_CAP)
     if rc:
         _raise(rc, err.value)
+
+
+def custom_ode_check(params: CustomOdeParams, math_mode: int = 0) -> str:
+    """pd_custom_ode_check: compile a run-time right-hand side for sm_100a without
+    a device; returns the compiler's log (warnings), raises EmitError on errors."""
+    log = ctypes.create_string_buffer(_ERR_CAP)
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_custom_ode_check(ctypes.byref(params), ctypes.sizeof(params), math_mode, log, _ERR_CAP, err,
+                                       _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    return log.value.decode("utf-8", "replace")

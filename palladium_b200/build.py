@@ -69,6 +69,11 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         return LIBRARY
     nvcc = _nvcc()
     BUILD_DIR.mkdir(exist_ok=True)
+    # pd_math.h as a string literal: the run-time compiled kernels include it from memory.
+    # Split into pieces below the 64 KiB a single literal may hold.
+    text = (CSRC / "pd_math.h").read_text()
+    pieces = [text[i:i + 8000] for i in range(0, len(text), 8000)]
+    (BUILD_DIR / "pd_math_embedded.inc").write_text("".join(f'R"PDMATH({piece})PDMATH"\n' for piece in pieces))
     extra = ["-Xptxas", "-v"] if verbose else []
     jobs: list[tuple[list[str], Path]] = []
     for mode, flags in MODE_FLAGS.items():
@@ -78,9 +83,11 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     jobs.append(([nvcc, *ARCH, *COMMON, "-c", str(CSRC / "pd_api.cu"), "-o", str(api_obj)], api_obj))
     noalloc_obj = BUILD_DIR / "pd_noalloc.o"
     jobs.append(([nvcc, *ARCH, *COMMON, "-c", str(CSRC / "pd_noalloc.cu"), "-o", str(noalloc_obj)], noalloc_obj))
+    rtc_obj = BUILD_DIR / "pd_rtc.o"
+    jobs.append(([nvcc, *ARCH, *COMMON, f"-I{BUILD_DIR}", "-c", str(CSRC / "pd_rtc.cu"), "-o", str(rtc_obj)], rtc_obj))
     with ThreadPoolExecutor(max_workers=len(jobs)) as pool:
         list(pool.map(lambda job: _run(job[0], verbose), jobs))
-    link = [nvcc, *ARCH, "-shared", "-o", str(LIBRARY), *[str(obj) for _, obj in jobs]]
+    link = [nvcc, *ARCH, "-shared", "-o", str(LIBRARY), *[str(obj) for _, obj in jobs], "-ldl"]
     _run(link, verbose)
     return LIBRARY
 

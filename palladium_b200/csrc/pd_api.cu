@@ -5,6 +5,7 @@
 // need, and launches them.  It never owns caller data.
 #include "../../include/palladium_cuda.h"
 #include "pd_kernels.h"
+#include "pd_rtc.h"
 
 #include <cuda_runtime.h>
 #include <math.h>
@@ -139,6 +140,7 @@ struct Plan {
     int64_t scratch_bytes = 0;
     int variant = 0;
     const void* kernel = nullptr;
+    PdRtcKernel rtc;               // run-time compiled families only
 };
 
 int requested_block(const int64_t block[3]) {
@@ -250,6 +252,23 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 if (g > needed) g = needed;
                 plan->grid[0] = g > 0 ? g : 1;
                 plan->scratch_bytes = 256;
+            }
+            return PD_OK;
+        }
+        case PD_FAMILY_CUSTOM_ODE: {
+            const pd_custom_ode_params* p;
+            int rc = get_params(params, params_bytes, &p, "custom_ode", err, err_cap);
+            if (rc) return rc;
+            rc = pd_rtc_check_params(p, err, err_cap);
+            if (rc) return rc;
+            const int b = req_block ? req_block : 128;
+            plan->kernel_name = pd_rtc_kernel_name(p);
+            plan->block[0] = b;
+            plan->grid[0] = (n + b - 1) / b;
+            if (dev.present) {
+                // compiled on the first use of this source text, cached afterwards
+                rc = pd_rtc_get(p, math_mode, dev.device, b, &plan->rtc, err, err_cap);
+                if (rc) return rc;
             }
             return PD_OK;
         }
@@ -435,6 +454,12 @@ int expected_sizes(int family, const void* params, const int64_t grid[3], std::v
         }
         case PD_FAMILY_KEPLER_RK4_DF32:
             in->assign(8, 4 * n); out->assign(8, 4 * n); return PD_OK;
+        case PD_FAMILY_CUSTOM_ODE: {
+            const pd_custom_ode_params* p = static_cast<const pd_custom_ode_params*>(params);
+            in->assign((size_t)(p->dim + p->nparam), 4 * n);
+            out->assign((size_t)(p->method == PD_ODE_RK4 ? p->dim : p->dim + 4), 4 * n);
+            return PD_OK;
+        }
         case PD_FAMILY_THREEFRY_BITS: {
             const pd_threefry_params* p = static_cast<const pd_threefry_params*>(params);
             in->assign(1, 8);
@@ -640,6 +665,25 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             PD_CUDA_TRY(pd_launch_threefry(a, b, st));
             break;
         }
+        case PD_FAMILY_CUSTOM_ODE: {
+            const pd_custom_ode_params* p = static_cast<const pd_custom_ode_params*>(params);
+            PdOdeArgs a;
+            memset(&a, 0, sizeof(a));
+            for (int i = 0; i < n_in; ++i) a.in[i] = (const float*)in[i];
+            for (int i = 0; i < n_out; ++i) a.out[i] = (float*)out[i];
+            a.n = n;
+            a.steps = (int)p->steps; a.max_steps = (int)p->max_steps;
+            a.h_half = (float)(0.5 * p->dt); a.h_full = (float)p->dt; a.h_sixth = (float)(p->dt / 6.0);
+            a.t1 = (float)p->t1; a.rtol = (float)p->rtol; a.atol = (float)p->atol; a.dt0 = (float)p->dt0;
+            a.safety = (float)p->safety; a.factor_min = (float)p->factor_min; a.factor_max = (float)p->factor_max;
+            if (p->method == PD_ODE_BS32) {
+                a.coeff1 = (float)((p->icoeff + p->pcoeff) / (double)p->error_order);
+                a.coeff2 = (float)(-p->pcoeff / (double)p->error_order);
+            }
+            rc = pd_rtc_launch(plan.rtc, plan.grid[0], b, a, (void*)st, err, err_cap);
+            if (rc) return rc;
+            break;
+        }
         default:
             return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "unknown kernel family %d", family);
     }
@@ -748,6 +792,7 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
     // count (the RNG key) is uploaded once and the chunk streams wait for it.
     const bool per_item_family = family == PD_FAMILY_LV_RK4 || family == PD_FAMILY_VDP_BS32 ||
                                  family == PD_FAMILY_LV_RK4_DF32 || family == PD_FAMILY_KEPLER_RK4_DF32 ||
+                                 family == PD_FAMILY_CUSTOM_ODE ||
                                  ((family == PD_FAMILY_GBM_THREEFRY || family == PD_FAMILY_GBM_PCG) && n_out == 1);
     const int64_t n = grid ? grid[0] : 0;
     const int64_t kMinChunked = (int64_t)1 << 18;
@@ -858,6 +903,11 @@ int pd_explain(int family, const void* params, size_t params_bytes, int math_mod
     info->static_smem_bytes = -1;
     info->dynamic_smem_bytes = 0;
     info->blocks_per_sm = -1;
+    if (dev.present && plan.rtc.function) {
+        info->regs_per_thread = plan.rtc.regs;
+        info->static_smem_bytes = plan.rtc.static_smem;
+        info->blocks_per_sm = plan.rtc.blocks_per_sm;
+    }
     if (dev.present && plan.kernel) {
         cudaFuncAttributes attr;
         if (cudaFuncGetAttributes(&attr, plan.kernel) == cudaSuccess) {

@@ -25,9 +25,17 @@
 #ifndef PD_MATH_H_
 #define PD_MATH_H_
 
+#if defined(__CUDACC_RTC__)
+// Run-time compilation has no host headers; the device math functions are built in.
+typedef unsigned int uint32_t;
+typedef int int32_t;
+typedef unsigned long long uint64_t;
+typedef long long int64_t;
+#else
 #include <stdint.h>
 #include <math.h>
 #include <string.h>
+#endif
 
 #if defined(__CUDACC__)
 #define PD_HD __host__ __device__ __forceinline__

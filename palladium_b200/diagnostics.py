@@ -79,14 +79,19 @@ def _normalise_threadgroup(threadgroup) -> tuple[int, ...] | None:
 
 def explain_spec(spec: KernelSpec, threadgroup=None, math_mode="fast") -> KernelDiagnostics:
     """Diagnostics for a validated call: asks the native library for the launch
-    plan; compiles and dispatches nothing."""
+    plan; dispatches nothing.  (A run-time right-hand side is compiled, and
+    cached, if a GPU is present: its register count is part of the report.)"""
     tg = _normalise_threadgroup(threadgroup)
+    if spec.family.name == "custom_ode":
+        lines = len(spec.family.constants["rhs"].splitlines())
+    else:
+        lines = _source_lines()
     info = _native.explain(spec.family.family_id, spec.params, math_mode_ordinal(math_mode), spec.grid, tg)
     return KernelDiagnostics(
         name=spec.name,
         grid=tuple(int(g) for g in spec.grid),
         threadgroup=tg,
-        msl_lines=_source_lines(),
+        msl_lines=lines,
         cuda_kernel=info.kernel_name.decode(),
         cuda_grid=tuple(int(v) for v in info.cuda_grid),
         cuda_block=tuple(int(v) for v in info.cuda_block),

@@ -30,6 +30,7 @@ __all__ = [
     "BlockInfo",
     "Family",
     "KernelSpec",
+    "custom_ode",
     "gbm_pcg",
     "gbm_threefry",
     "gray_scott",
@@ -118,6 +119,63 @@ def vdp_bs32(t1: float = 10.0, rtol: float = 1e-5, atol: float = 1e-7, dt0: floa
                                    max_steps=int(max_steps), pcoeff=float(pcoeff), icoeff=float(icoeff),
                                    safety=float(safety), factor_min=float(factor_min),
                                    factor_max=float(factor_max), error_order=int(error_order)), pallas_fn)
+
+
+_CHECKED_SOURCES: set = set()
+
+
+def custom_ode(rhs: str, dim: int, nparam: int = 0, *, method: str = "rk4", dt: float = 0.01, steps: int = 500,
+               t1: float = 10.0, rtol: float = 1e-5, atol: float = 1e-7, dt0: float = 0.01, max_steps: int = 6000,
+               pcoeff: float = 0.4, icoeff: float = 0.3, safety: float = 0.9, factor_min: float = 0.2,
+               factor_max: float = 10.0, error_order: int = 3, check: bool = True,
+               pallas_fn: Callable | None = None) -> Family:
+    """An ensemble of independent systems y' = f(t, y, p) with a right-hand side
+    of the caller's: the open end of the family set, where the reference lets a
+    user write any Pallas function (and register lowering rules for what its
+    emitter lacks, docs/extending.md:1-69).
+
+    `rhs` is CUDA C: the statements of
+    `void rhs(float t, const float* y, const float* p, float* dy)`, e.g.
+    `"dy[0] = y[1]; dy[1] = (p[0] * (1.0f - y[0] * y[0])) * y[1] - y[0];"`.
+    It is compiled at run time (NVRTC) under the flag set of the call's math
+    mode and cached by source text, the way the reference compiles the MSL it
+    emits on a cache miss (src/palladium/__init__.py:146-158).
+
+    method="rk4": `steps` classic RK4 steps of `dt`; grid=(N,), inputs are the
+    `dim` state arrays then the `nparam` parameter arrays, outputs the `dim`
+    final states (all (N,) float32).  With the Lotka-Volterra right-hand side
+    this reproduces `lv_rk4` bit for bit under MathMode.SAFE.
+    method="bs32": adaptive Bogacki-Shampine 3(2) with the controller, counters
+    and stall semantics of `vdp_bs32`; outputs t, the `dim` states, steps,
+    rejected, real.
+
+    With `check` (default) the source is compiled once here, without a GPU, so a
+    faulty right-hand side raises EmitError where it is defined."""
+    if method not in ("rk4", "bs32"):
+        raise TraceError(f"custom_ode: method must be 'rk4' or 'bs32', got {method!r}")
+    if not isinstance(rhs, str) or not rhs.strip():
+        raise TraceError("custom_ode: rhs must be a non-empty string of CUDA C statements")
+    if not 1 <= int(dim) <= 8:
+        raise TraceError(f"custom_ode: dim must lie in [1, 8], got {dim}")
+    if not 0 <= int(nparam) <= 8:
+        raise TraceError(f"custom_ode: nparam must lie in [0, 8], got {nparam}")
+    fam = Family("custom_ode", dict(rhs=rhs, dim=int(dim), nparam=int(nparam), method=method, dt=float(dt),
+                                    steps=int(steps), t1=float(t1), rtol=float(rtol), atol=float(atol),
+                                    dt0=float(dt0), max_steps=int(max_steps), pcoeff=float(pcoeff),
+                                    icoeff=float(icoeff), safety=float(safety), factor_min=float(factor_min),
+                                    factor_max=float(factor_max), error_order=int(error_order)), pallas_fn)
+    key = (rhs, int(dim), int(nparam), method)
+    if check and key not in _CHECKED_SOURCES:
+        _native.custom_ode_check(_custom_ode_params(fam.constants))
+        _CHECKED_SOURCES.add(key)
+    return fam
+
+
+def _custom_ode_params(c: dict) -> "_native.CustomOdeParams":
+    return _native.CustomOdeParams(c["rhs"].encode(), c["dim"], c["nparam"], 0 if c["method"] == "rk4" else 1,
+                                   c["dt"], c["steps"], c["t1"], c["rtol"], c["atol"], c["dt0"], c["pcoeff"],
+                                   c["icoeff"], c["safety"], c["factor_min"], c["factor_max"], c["error_order"],
+                                   c["max_steps"])
 
 
 def gbm_threefry(s0: float = 100.0, strike: float = 105.0, r: float = 0.03, sigma: float = 0.2, t: float = 1.0,
@@ -351,6 +409,17 @@ def trace(family: Family, call_kwargs: dict[str, Any], *args) -> KernelSpec:
         blocks_in = [_per_item(n)] * 8
         blocks_out = [_per_item(n)] * 8
         params = _native.KeplerRk4Df32Params(c["dt"], c["gm"], c["steps"])
+    elif name == "custom_ode":
+        if len(grid) != 1:
+            raise TraceError(f"{name}: grid must be (N,), got {grid}")
+        n = grid[0]
+        n_in = c["dim"] + c["nparam"]
+        n_out = c["dim"] if c["method"] == "rk4" else c["dim"] + 4
+        inputs = tuple(vec(n) for _ in range(n_in))
+        outputs = tuple(vec(n) for _ in range(n_out))
+        blocks_in = [_per_item(n)] * n_in
+        blocks_out = [_per_item(n)] * n_out
+        params = _custom_ode_params(c)
     elif name == "threefry_bits":
         if len(grid) != 1:
             raise TraceError(f"{name}: grid must be (N,), got {grid}")

@@ -80,3 +80,11 @@ def threefry_solver(op, n, count=1, call=None):
     else:
         out = shaped(n, count)
     return (call or pd.cuda_call)(fam, grid=(n,), out_shape=out, math_mode=pd.MathMode.SAFE)
+
+
+def custom_solver(n, rhs, dim, nparam, call=None, math_mode=pd.MathMode.SAFE, **constants):
+    """A run-time right-hand side behind the usual call shape."""
+    fam = families.custom_ode(rhs, dim, nparam, **constants)
+    n_out = dim if fam.constants["method"] == "rk4" else dim + 4
+    return (call or pd.cuda_call)(fam, grid=(n,), in_specs=[SPEC_1] * (dim + nparam), out_specs=(SPEC_1,) * n_out,
+                                  out_shape=tuple(shaped(n) for _ in range(n_out)), math_mode=math_mode)

@@ -1,0 +1,66 @@
+"""Run-time right-hand sides, the parts that need no GPU: the definition-time
+compile check (NVRTC runs without a device), call validation, and the generic
+oracle loops against the family-specific ones (which carry the pins)."""
+
+import numpy as np
+import pytest
+
+import oracle
+import palladium_b200 as pd
+from oracle import custom_ode as oracle_custom
+from palladium_b200 import families, pl
+from palladium_b200 import workloads as W
+
+LV = "dy[0] = p[0]*y[0] - (p[1]*y[0])*y[1];\ndy[1] = (p[2]*y[0])*y[1] - p[3]*y[1];"
+VDP = "dy[0] = y[1];\ndy[1] = (p[0]*(1.0f - y[0]*y[0]))*y[1] - y[0];"
+
+
+def test_generic_oracle_loops_equal_the_pinned_family_oracles():
+    ins = W.lotka_volterra_ensemble(500)
+    got = oracle_custom.rk4(LV, 2, 4, ins, dt=0.01, steps=300)
+    want = oracle.lv_rk4(*ins, dt=0.01, steps=300)
+    for g, w in zip(got, want):
+        np.testing.assert_array_equal(g, w)
+    x0, v0, mu = W.van_der_pol_ensemble(100)
+    cfg = dict(t1=2.0, rtol=1e-5, atol=1e-7, dt0=0.01, max_steps=3000)
+    for flavour in ("pd", "libm"):
+        got = oracle_custom.bs32(VDP, 2, 1, (x0, v0, mu), pow=flavour, **cfg)
+        want = oracle.vdp_bs32(x0, v0, mu, pow=flavour, **cfg)
+        for g, w in zip(got, want):
+            np.testing.assert_array_equal(g, w)
+
+
+def test_a_faulty_right_hand_side_fails_where_it_is_defined():
+    with pytest.raises(pd.EmitError, match=r'rhs\(2\): error: identifier "q" is undefined'):
+        families.custom_ode("dy[0] = y[0];\ndy[1] = q;", 2)
+    # the check can be skipped (the error then surfaces at the first launch)
+    families.custom_ode("dy[0] = q;", 1, check=False)
+
+
+def test_constructor_argument_checks():
+    with pytest.raises(pd.TraceError, match="method"):
+        families.custom_ode(LV, 2, 4, method="euler")
+    with pytest.raises(pd.TraceError, match="dim"):
+        families.custom_ode(LV, 9, 0, check=False)
+    with pytest.raises(pd.TraceError, match="nparam"):
+        families.custom_ode(LV, 2, 9, check=False)
+    with pytest.raises(pd.TraceError, match="non-empty"):
+        families.custom_ode("  ", 2, 4)
+
+
+def test_call_shape_is_validated_like_any_family():
+    n = 64
+    sh = pl.ShapeDtypeStruct((n,), np.float32)
+    fam = families.custom_ode(LV, 2, 4, dt=0.01, steps=10)
+    spec = families.trace(fam, dict(grid=(n,), out_shape=(sh, sh)))
+    assert len(spec.inputs) == 6 and len(spec.outputs) == 2
+    with pytest.raises(pd.TraceError, match="produces 2"):
+        families.trace(fam, dict(grid=(n,), out_shape=(sh,)))
+    adaptive = families.custom_ode(VDP, 2, 1, method="bs32")
+    spec = families.trace(adaptive, dict(grid=(n,), out_shape=(sh,) * 6))
+    assert len(spec.inputs) == 3 and len(spec.outputs) == 6
+    call = pd.cuda_call(fam, grid=(n,), out_shape=(sh, sh))
+    with pytest.raises(pd.DispatchError):
+        call(*[np.zeros(n, np.float64)] * 6)
+    report = call.explain(*[np.zeros(n, np.float32)] * 6)
+    assert "pd_ode_rk4" in str(report)
