@@ -249,7 +249,12 @@ def _shape_dtype(x) -> tuple[tuple[int, ...], np.dtype]:
     if shape is None or dtype is None:
         arr = np.asarray(x)
         shape, dtype = arr.shape, arr.dtype
-    return tuple(int(s) for s in shape), np.dtype(dtype)
+    try:
+        dtype = np.dtype(dtype)
+    except TypeError:
+        # a torch dtype: "torch.float32" -> float32
+        dtype = np.dtype(str(dtype).rsplit(".", 1)[-1])
+    return tuple(int(s) for s in shape), dtype
 
 
 def _as_list(x) -> list:
