@@ -62,7 +62,9 @@ typedef enum pd_family {
     PD_FAMILY_GBM_PCG = 7,       /* gbm_paths with pcg_hash, the hand-written kernel GBM_MSL, examples/03_sde_montecarlo.py:34-70 */
     PD_FAMILY_CUSTOM_ODE = 8,    /* a caller-supplied right-hand side, compiled at run time: the counterpart of
                                     handing the handler MSL source + entry-point name, native/ffi/palladium_ffi.cpp:136-148 */
-    PD_FAMILY_COUNT = 9
+    PD_FAMILY_SOURCE = 9,        /* a complete caller-written kernel: source text + entry-point name, the
+                                    attributes of the reference handler itself, native/ffi/palladium_ffi.cpp:110-117 */
+    PD_FAMILY_COUNT = 10
 } pd_family;
 
 /* ---- per-family parameter blocks (passed by pointer + sizeof) ------------ */
@@ -171,6 +173,24 @@ typedef struct pd_custom_ode_params {
     int64_t max_steps;
 } pd_custom_ode_params;
 
+/* A complete kernel of the caller's, as CUDA C source: what the reference's
+ * handler receives as `msl_source` + `function_name` (palladium_ffi.cpp:110-117),
+ * compiled on the first use of a (source, name, math mode) and kept for the
+ * life of the process (:44-49,75-84).  The kernel must be declared
+ *     extern "C" __global__ void <function_name>(T0* b0, ..., Tk* bk,
+ *                                                long long gx, long long gy, long long gz)
+ * with one pointer per buffer in binding order -- inputs first, then outputs,
+ * the order the reference binds them (:128-148) -- followed by the extents of
+ * the logical grid.  One thread is launched per grid point, rounded up to whole
+ * blocks, so the kernel returns when (PD_THREAD_X, PD_THREAD_Y, PD_THREAD_Z)
+ * lies outside (gx, gy, gz); those macros and pd_math.h are in scope.
+ * `block` is the threadgroup; (0,0,0) lets the library choose (:158-162).
+ * Buffer sizes are the caller's business: none are checked. */
+typedef struct pd_source_kernel_params {
+    const char* cuda_source;     /* NUL-terminated; must stay valid for the call only */
+    const char* function_name;   /* at most 63 bytes */
+} pd_source_kernel_params;
+
 /* ---- launch geometry report (the `.explain()` payload) -------------------- */
 typedef struct pd_launch_info {
     char kernel_name[64];
@@ -191,6 +211,10 @@ typedef struct pd_launch_info {
  * before any dispatch).  `log` receives the compiler's messages. */
 PD_API int pd_custom_ode_check(const pd_custom_ode_params* params, size_t params_bytes, int math_mode,
                                char* log, size_t log_cap, char* err, size_t err_cap);
+
+/* The same for a PD_FAMILY_SOURCE kernel. */
+PD_API int pd_source_kernel_check(const pd_source_kernel_params* params, size_t params_bytes, int math_mode,
+                                  char* log, size_t log_cap, char* err, size_t err_cap);
 
 /* ABI version of the loaded library (== PD_ABI_VERSION it was built with). */
 PD_API int pd_version(void);

@@ -50,6 +50,7 @@ EXPORTED_SYMBOLS = (
     "pd_last_kernel_ms",
     "pd_gray_scott_static",
     "pd_custom_ode_check",
+    "pd_source_kernel_check",
 )
 
 FAMILY_IDS = {
@@ -62,6 +63,7 @@ FAMILY_IDS = {
     "threefry_bits": 6,
     "gbm_pcg": 7,
     "custom_ode": 8,
+    "source": 9,
 }
 
 _i64 = ctypes.c_int64
@@ -105,6 +107,10 @@ class CustomOdeParams(ctypes.Structure):
                 ("steps", _i64), ("t1", _dbl), ("rtol", _dbl), ("atol", _dbl), ("dt0", _dbl), ("pcoeff", _dbl),
                 ("icoeff", _dbl), ("safety", _dbl), ("factor_min", _dbl), ("factor_max", _dbl),
                 ("error_order", _i64), ("max_steps", _i64)]
+
+
+class SourceKernelParams(ctypes.Structure):
+    _fields_ = [("cuda_source", ctypes.c_char_p), ("function_name", ctypes.c_char_p)]
 
 
 class LaunchInfo(ctypes.Structure):
@@ -155,6 +161,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pd_gray_scott_static.argtypes = [ctypes.POINTER(GrayScottParams), ci, vp, vp, vp, vp, vp, cp, sz]
     lib.pd_custom_ode_check.restype = ci
     lib.pd_custom_ode_check.argtypes = [ctypes.POINTER(CustomOdeParams), sz, ci, cp, sz, cp, sz]
+    lib.pd_source_kernel_check.restype = ci
+    lib.pd_source_kernel_check.argtypes = [ctypes.POINTER(SourceKernelParams), sz, ci, cp, sz, cp, sz]
 
 
 def library() -> ctypes.CDLL:
@@ -311,6 +319,17 @@ def custom_ode_check(params: CustomOdeParams, math_mode: int = 0) -> str:
     err = ctypes.create_string_buffer(_ERR_CAP)
     rc = library().pd_custom_ode_check(ctypes.byref(params), ctypes.sizeof(params), math_mode, log, _ERR_CAP, err,
                                        _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    return log.value.decode("utf-8", "replace")
+
+
+def source_kernel_check(params: SourceKernelParams, math_mode: int = 0) -> str:
+    """pd_source_kernel_check: the same for a complete caller-written kernel."""
+    log = ctypes.create_string_buffer(_ERR_CAP)
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_source_kernel_check(ctypes.byref(params), ctypes.sizeof(params), math_mode, log, _ERR_CAP, err,
+                                          _ERR_CAP)
     if rc:
         _raise(rc, err.value)
     return log.value.decode("utf-8", "replace")

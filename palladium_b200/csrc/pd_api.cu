@@ -194,7 +194,7 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
         if (grid[i] < 0) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "grid[%d] is negative", i);
     const PdModeTable* mt = mode_table(math_mode);
     const int req_block = requested_block(block);
-    if (req_block) {
+    if (req_block && family != PD_FAMILY_SOURCE) {
         int rc = check_block(req_block, err, err_cap);
         if (rc) return rc;
     }
@@ -268,6 +268,43 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
             if (dev.present) {
                 // compiled on the first use of this source text, cached afterwards
                 rc = pd_rtc_get(p, math_mode, dev.device, b, &plan->rtc, err, err_cap);
+                if (rc) return rc;
+            }
+            return PD_OK;
+        }
+        case PD_FAMILY_SOURCE: {
+            const pd_source_kernel_params* p;
+            int rc = get_params(params, params_bytes, &p, "source kernel", err, err_cap);
+            if (rc) return rc;
+            rc = pd_rtc_check_source(p, err, err_cap);
+            if (rc) return rc;
+            // One thread per point of the logical grid, as Metal's dispatchThreads launches
+            // them; whole blocks here, the kernel trims the edge itself.
+            int64_t b[3];
+            if (req_block) {
+                for (int i = 0; i < 3; ++i) b[i] = block[i] > 0 ? block[i] : 1;
+                if (b[0] * b[1] * b[2] > 1024 || b[2] > 64)
+                    return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                                "threadgroup (%lld, %lld, %lld) exceeds 1024 threads (or 64 in z)", (long long)b[0],
+                                (long long)b[1], (long long)b[2]);
+            } else if (grid[1] <= 1 && grid[2] <= 1) {
+                b[0] = 128; b[1] = 1; b[2] = 1;
+            } else if (grid[2] <= 1) {
+                b[0] = 32; b[1] = 4; b[2] = 1;
+            } else {
+                b[0] = 32; b[1] = 2; b[2] = 2;
+            }
+            for (int i = 0; i < 3; ++i) {
+                const int64_t g = grid[i] > 0 ? grid[i] : (i == 0 ? 0 : 1);
+                plan->block[i] = b[i];
+                plan->grid[i] = (g + b[i] - 1) / b[i];
+            }
+            if (plan->grid[1] > 65535 || plan->grid[2] > 65535)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                            "grid needs more than 65535 blocks in y or z; put the long axis first");
+            plan->kernel_name = p->function_name;
+            if (dev.present) {
+                rc = pd_rtc_get_source(p, math_mode, dev.device, (int)(b[0] * b[1] * b[2]), &plan->rtc, err, err_cap);
                 if (rc) return rc;
             }
             return PD_OK;
@@ -492,14 +529,23 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
     Plan plan;
     int rc = build_plan(family, params, params_bytes, math_mode, grid, block, vec_ok, dev, &plan, err, err_cap);
     if (rc) return rc;
-    std::vector<size_t> want_in, want_out;
-    rc = expected_sizes(family, params, grid, &want_in, &want_out, n_out, err, err_cap);
-    if (rc) return rc;
-    rc = check_buffers("input", n_in, (int)want_in.size(), in_bytes, want_in.data(), in, err, err_cap);
-    if (rc) return rc;
-    rc = check_buffers("output", n_out, (int)want_out.size(), out_bytes, want_out.data(),
-                       const_cast<const void* const*>(out), err, err_cap);
-    if (rc) return rc;
+    if (family != PD_FAMILY_SOURCE) {   // a caller-written kernel defines its own buffer sizes
+        std::vector<size_t> want_in, want_out;
+        rc = expected_sizes(family, params, grid, &want_in, &want_out, n_out, err, err_cap);
+        if (rc) return rc;
+        rc = check_buffers("input", n_in, (int)want_in.size(), in_bytes, want_in.data(), in, err, err_cap);
+        if (rc) return rc;
+        rc = check_buffers("output", n_out, (int)want_out.size(), out_bytes, want_out.data(),
+                           const_cast<const void* const*>(out), err, err_cap);
+        if (rc) return rc;
+    } else {
+        if (n_in + n_out > 64)
+            return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "source kernel: at most 64 buffers, got %d", n_in + n_out);
+        for (int i = 0; i < n_in; ++i)
+            if (in_bytes[i] && !in[i]) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "input %d: NULL pointer", i);
+        for (int i = 0; i < n_out; ++i)
+            if (out_bytes[i] && !out[i]) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output %d: NULL pointer", i);
+    }
 
     void* scratch = nullptr;
     if (plan.scratch_bytes > 0) {
@@ -663,6 +709,16 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             a.data = p->op == 2 ? (const uint32_t*)in[1] : nullptr;
             a.out = out[0]; a.n = n; a.count = p->count; a.op = (int)p->op;
             PD_CUDA_TRY(pd_launch_threefry(a, b, st));
+            break;
+        }
+        case PD_FAMILY_SOURCE: {
+            std::vector<void*> buffers;
+            for (int i = 0; i < n_in; ++i) buffers.push_back(const_cast<void*>(in[i]));
+            for (int i = 0; i < n_out; ++i) buffers.push_back(out[i]);
+            const int64_t logical[3] = {grid[0], grid[1] > 0 ? grid[1] : 1, grid[2] > 0 ? grid[2] : 1};
+            rc = pd_rtc_launch_source(plan.rtc, plan.grid, plan.block, logical, (int)buffers.size(), buffers.data(),
+                                      (void*)st, err, err_cap);
+            if (rc) return rc;
             break;
         }
         case PD_FAMILY_CUSTOM_ODE: {

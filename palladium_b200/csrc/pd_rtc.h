@@ -55,4 +55,14 @@ int pd_rtc_launch(const PdRtcKernel& k, long long grid, int block, const PdOdeAr
 
 const char* pd_rtc_kernel_name(const pd_custom_ode_params* p);
 
+// Caller-written kernels (PD_FAMILY_SOURCE): the same compile / cache / load path
+// on complete CUDA source; the kernel takes one pointer per buffer (inputs, then
+// outputs) followed by the three extents of the logical grid.
+int pd_rtc_check_source(const pd_source_kernel_params* p, char* err, size_t err_cap);
+int pd_rtc_get_source(const pd_source_kernel_params* p, int math_mode, int device, int block, PdRtcKernel* out,
+                      char* err, size_t err_cap);
+int pd_rtc_launch_source(const PdRtcKernel& k, const int64_t cuda_grid[3], const int64_t block[3],
+                         const int64_t logical_grid[3], int n_buffers, void* const* buffers, void* stream, char* err,
+                         size_t err_cap);
+
 #endif  // PD_RTC_H_

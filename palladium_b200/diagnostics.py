@@ -84,6 +84,8 @@ def explain_spec(spec: KernelSpec, threadgroup=None, math_mode="fast") -> Kernel
     tg = _normalise_threadgroup(threadgroup)
     if spec.family.name == "custom_ode":
         lines = len(spec.family.constants["rhs"].splitlines())
+    elif spec.family.name == "source":
+        lines = len(spec.family.constants["source"].splitlines())
     else:
         lines = _source_lines()
     info = _native.explain(spec.family.family_id, spec.params, math_mode_ordinal(math_mode), spec.grid, tg)

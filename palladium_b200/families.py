@@ -37,6 +37,7 @@ __all__ = [
     "kepler_rk4_df32",
     "lv_rk4",
     "lv_rk4_df32",
+    "source_kernel",
     "threefry_bits",
     "trace",
     "vdp_bs32",
@@ -176,6 +177,34 @@ def _custom_ode_params(c: dict) -> "_native.CustomOdeParams":
                                    c["dt"], c["steps"], c["t1"], c["rtol"], c["atol"], c["dt0"], c["pcoeff"],
                                    c["icoeff"], c["safety"], c["factor_min"], c["factor_max"], c["error_order"],
                                    c["max_steps"])
+
+
+def source_kernel(source: str, function_name: str, check: bool = True) -> Family:
+    """A complete kernel of your own as CUDA C source: what `metal_call` hands
+    its runtime as emitted MSL plus an entry-point name
+    (src/palladium/dispatch.py:286-292), written by hand here because there is
+    no Pallas-to-CUDA emitter.
+
+    The kernel is declared
+    `extern "C" __global__ void name(T0* b0, ..., Tk* bk, long long gx, long long gy, long long gz)`:
+    one pointer per array in call order (inputs, then the outputs of
+    `out_shape`), then the extents of `grid`.  One thread runs per grid point,
+    rounded up to whole blocks: return when `PD_THREAD_X >= gx` (and likewise
+    `PD_THREAD_Y`, `PD_THREAD_Z`).  `pd_math.h` (Threefry, df32, `pd_powf`) is
+    in scope.  Compiled at run time under the call's math mode, cached by
+    source; array shapes and dtypes are whatever the call passes, unchecked
+    against the kernel, as with hand-written MSL."""
+    if not isinstance(source, str) or not source.strip():
+        raise TraceError("source_kernel: source must be a non-empty string of CUDA C")
+    if not isinstance(function_name, str) or not function_name.isidentifier() or len(function_name) > 63:
+        raise TraceError(f"source_kernel: function_name must be a C identifier of at most 63 characters, "
+                         f"got {function_name!r}")
+    fam = Family("source", dict(source=source, function_name=function_name))
+    key = ("source", source, function_name)
+    if check and key not in _CHECKED_SOURCES:
+        _native.source_kernel_check(_native.SourceKernelParams(source.encode(), function_name.encode()))
+        _CHECKED_SOURCES.add(key)
+    return fam
 
 
 def gbm_threefry(s0: float = 100.0, strike: float = 105.0, r: float = 0.03, sigma: float = 0.2, t: float = 1.0,
@@ -425,6 +454,14 @@ def trace(family: Family, call_kwargs: dict[str, Any], *args) -> KernelSpec:
         blocks_in = [_per_item(n)] * n_in
         blocks_out = [_per_item(n)] * n_out
         params = _custom_ode_params(c)
+    elif name == "source":
+        if not 1 <= len(grid) <= 3:
+            raise TraceError(f"{name}: grid must have 1 to 3 dimensions, got {grid}")
+        # the kernel defines its own operands: take them as the call gives them
+        inputs = tuple(BlockInfo(shape, shape, dtype) for shape, dtype in (_shape_dtype(a) for a in args))
+        outputs = tuple(BlockInfo(shape, shape, dtype) for shape, dtype in outs)
+        blocks_in = blocks_out = None
+        params = _native.SourceKernelParams(c["source"].encode(), c["function_name"].encode())
     elif name == "threefry_bits":
         if len(grid) != 1:
             raise TraceError(f"{name}: grid must be (N,), got {grid}")

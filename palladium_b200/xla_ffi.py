@@ -23,6 +23,7 @@ from . import _native
 from .errors import EmitError
 
 _TARGET_NAME = "palladium_cuda_dispatch"
+_SOURCE_TARGET_NAME = "palladium_cuda_dispatch_source"
 _PKG = Path(__file__).resolve().parent
 _SHIM = _PKG / "libpalladium_xla_ffi.so"
 _REGISTER_LOCK = threading.Lock()
@@ -58,6 +59,8 @@ def _register() -> None:
         _native.library()
         handle = ctypes.CDLL(str(_SHIM))
         jax.ffi.register_ffi_target(_TARGET_NAME, jax.ffi.pycapsule(handle.palladium_cuda_dispatch), platform="cpu")
+        jax.ffi.register_ffi_target(_SOURCE_TARGET_NAME, jax.ffi.pycapsule(handle.palladium_cuda_dispatch_source),
+                                    platform="cpu")
         _registered = True
 
 
@@ -74,7 +77,16 @@ def ffi_call(callable_, args):
     out_structs = [jax.ShapeDtypeStruct(info.array_shape, info.dtype) for info in spec.outputs]
     result_shapes = out_structs[0] if len(out_structs) == 1 else out_structs
     params = np.frombuffer(bytes(spec.params), dtype=np.uint8)
-    return jax.ffi.ffi_call(_TARGET_NAME, result_shapes, vmap_method=callable_._vmap_method)(
-        *args, family=np.int64(spec.family.family_id), params=params, grid_x=np.int64(grid[0]),
+    target, text = _TARGET_NAME, {}
+    constants = spec.family.constants
+    if spec.family.name == "source":
+        # source text travels as string attributes, as msl_source / function_name do in the reference
+        target = _SOURCE_TARGET_NAME
+        text = dict(cuda_source=constants["source"], function_name=constants["function_name"])
+    elif spec.family.name == "custom_ode":
+        target = _SOURCE_TARGET_NAME
+        text = dict(cuda_source=constants["rhs"], function_name="")
+    return jax.ffi.ffi_call(target, result_shapes, vmap_method=callable_._vmap_method)(
+        *args, **text, family=np.int64(spec.family.family_id), params=params, grid_x=np.int64(grid[0]),
         grid_y=np.int64(grid[1]), grid_z=np.int64(grid[2]), threadgroup_x=np.int64(tg[0]),
         threadgroup_y=np.int64(tg[1]), threadgroup_z=np.int64(tg[2]), math_mode=np.int64(callable_._math_mode))

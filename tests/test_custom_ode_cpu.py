@@ -64,3 +64,38 @@ def test_call_shape_is_validated_like_any_family():
         call(*[np.zeros(n, np.float64)] * 6)
     report = call.explain(*[np.zeros(n, np.float32)] * 6)
     assert "pd_ode_rk4" in str(report)
+
+
+# ------------------------------------------------------------------ complete caller-written kernels
+SAXPY = '''
+extern "C" __global__ void saxpy(const float* a, const float* x, const float* y, float* out,
+                                 long long gx, long long gy, long long gz) {
+    const long long i = PD_THREAD_X;
+    if (i >= gx) return;
+    out[i] = a[0] * x[i] + y[i];
+}
+'''
+
+
+def test_source_kernel_is_checked_where_it_is_defined():
+    families.source_kernel(SAXPY, "saxpy")
+    with pytest.raises(pd.EmitError, match=r'source\(6\): error: identifier "b" is undefined'):
+        families.source_kernel(SAXPY.replace("a[0]", "b[0]"), "saxpy")
+    with pytest.raises(pd.TraceError, match="C identifier"):
+        families.source_kernel(SAXPY, "not a name")
+    with pytest.raises(pd.TraceError, match="non-empty"):
+        families.source_kernel("", "saxpy")
+
+
+def test_source_kernel_takes_its_operands_from_the_call():
+    n = 1000
+    fam = families.source_kernel(SAXPY, "saxpy")
+    args = (np.ones(1, np.float32), np.zeros(n, np.float32), np.zeros(n, np.float32))
+    spec = families.trace(fam, dict(grid=(n,), out_shape=pl.ShapeDtypeStruct((n,), np.float32)), *args)
+    assert [i.array_shape for i in spec.inputs] == [(1,), (n,), (n,)] and spec.outputs[0].array_shape == (n,)
+    call = pd.cuda_call(fam, grid=(n,), out_shape=pl.ShapeDtypeStruct((n,), np.float32), threadgroup=(64,))
+    report = call.explain(*args)
+    assert report.cuda_kernel == "saxpy" and report.cuda_grid == (16, 1, 1) and report.cuda_block == (64, 1, 1)
+    assert report.msl_lines == len(SAXPY.splitlines())
+    with pytest.raises(pd.TraceError, match="1 to 3 dimensions"):
+        families.trace(fam, dict(grid=(2, 2, 2, 2), out_shape=pl.ShapeDtypeStruct((n,), np.float32)), *args)
