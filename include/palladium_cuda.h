@@ -212,6 +212,14 @@ typedef struct pd_launch_info {
 PD_API int pd_custom_ode_check(const pd_custom_ode_params* params, size_t params_bytes, int math_mode,
                                char* log, size_t log_cap, char* err, size_t err_cap);
 
+/* The text handed to the compiler for a PD_FAMILY_CUSTOM_ODE call (defines,
+ * shared prologue, the right-hand side, the integrator kernel): what the
+ * reference's `debug_msl` shows of an emitted kernel
+ * (src/palladium/__init__.py:162-190).  `needed` receives the size including the
+ * terminating NUL; the text is truncated to out_cap. */
+PD_API int pd_custom_ode_source(const pd_custom_ode_params* params, size_t params_bytes, int math_mode,
+                                char* out, size_t out_cap, size_t* needed, char* err, size_t err_cap);
+
 /* The same for a PD_FAMILY_SOURCE kernel. */
 PD_API int pd_source_kernel_check(const pd_source_kernel_params* params, size_t params_bytes, int math_mode,
                                   char* log, size_t log_cap, char* err, size_t err_cap);

@@ -160,13 +160,23 @@ class CudaCallable:
 
 def debug_msl(kernel: Family, *example_args, **pallas_kwargs) -> str:
     """The reference returns the emitted MSL for a call
-    (src/palladium/__init__.py:162-190).  The kernels here are precompiled, so
-    the text returned is the launch record: kernel name, constants, CUDA launch
-    geometry and the source file the kernel is built from."""
+    (src/palladium/__init__.py:162-190).  For the run-time compiled families
+    the text returned is the CUDA source handed to the compiler (the generated
+    integrator around a `custom_ode` right-hand side; a `source_kernel`'s own
+    text).  The other kernels are precompiled, so for them it is the launch
+    record: kernel name, constants, CUDA launch geometry and the source file
+    the kernel is built from."""
+    from . import _native
+    from .math_mode import math_mode_ordinal
+
     math_mode = pallas_kwargs.pop("math_mode", MathMode.FAST)
     threadgroup = pallas_kwargs.pop("threadgroup", None)
     spec = trace(kernel, pallas_kwargs, *example_args)
     diag = explain_spec(spec, threadgroup, math_mode)
+    if kernel.name == "custom_ode":
+        return f"// {diag}\n" + _native.custom_ode_source(spec.params, math_mode_ordinal(math_mode))
+    if kernel.name == "source":
+        return f"// {diag}\n" + kernel.constants["source"]
     return (f"// {diag}\n// family: {kernel.name}\n// constants: {kernel.constants}\n"
             f"// source: palladium_b200/csrc/pd_kernels.cu\n")
 

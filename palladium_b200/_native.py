@@ -51,6 +51,7 @@ EXPORTED_SYMBOLS = (
     "pd_gray_scott_static",
     "pd_custom_ode_check",
     "pd_source_kernel_check",
+    "pd_custom_ode_source",
 )
 
 FAMILY_IDS = {
@@ -161,6 +162,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pd_gray_scott_static.argtypes = [ctypes.POINTER(GrayScottParams), ci, vp, vp, vp, vp, vp, cp, sz]
     lib.pd_custom_ode_check.restype = ci
     lib.pd_custom_ode_check.argtypes = [ctypes.POINTER(CustomOdeParams), sz, ci, cp, sz, cp, sz]
+    lib.pd_custom_ode_source.restype = ci
+    lib.pd_custom_ode_source.argtypes = [ctypes.POINTER(CustomOdeParams), sz, ci, cp, sz, szp, cp, sz]
     lib.pd_source_kernel_check.restype = ci
     lib.pd_source_kernel_check.argtypes = [ctypes.POINTER(SourceKernelParams), sz, ci, cp, sz, cp, sz]
 
@@ -333,3 +336,20 @@ def source_kernel_check(params: SourceKernelParams, math_mode: int = 0) -> str:
     if rc:
         _raise(rc, err.value)
     return log.value.decode("utf-8", "replace")
+
+
+def custom_ode_source(params: CustomOdeParams, math_mode: int = 2) -> str:
+    """pd_custom_ode_source: the generated CUDA text of a run-time right-hand side call."""
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    needed = ctypes.c_size_t(0)
+    lib = library()
+    rc = lib.pd_custom_ode_source(ctypes.byref(params), ctypes.sizeof(params), math_mode, None, 0,
+                                  ctypes.byref(needed), err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    out = ctypes.create_string_buffer(needed.value)
+    rc = lib.pd_custom_ode_source(ctypes.byref(params), ctypes.sizeof(params), math_mode, out, needed.value, None,
+                                  err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    return out.value.decode("utf-8", "replace")

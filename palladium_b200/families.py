@@ -10,6 +10,11 @@ that the `grid` / `in_specs` / `out_specs` / `out_shape` of the call describe
 the launch that family performs -- the same keywords, with the same meaning, a
 user of the reference already writes for `metal_call`.
 
+Two families are open-ended and compiled at run time, as the reference compiles
+the MSL it emits: `custom_ode` (a right-hand side of the caller's inside the
+library's RK4 or adaptive loop) and `source_kernel` (a complete CUDA kernel of
+the caller's).
+
 `trace(family, call_kwargs, *args)` produces the `KernelSpec` analogue: name,
 grid, and one `BlockInfo` per operand.
 """

@@ -99,3 +99,15 @@ def test_source_kernel_takes_its_operands_from_the_call():
     assert report.msl_lines == len(SAXPY.splitlines())
     with pytest.raises(pd.TraceError, match="1 to 3 dimensions"):
         families.trace(fam, dict(grid=(2, 2, 2, 2), out_shape=pl.ShapeDtypeStruct((n,), np.float32)), *args)
+
+
+def test_debug_msl_shows_the_text_handed_to_the_compiler():
+    n = 8
+    sh = pl.ShapeDtypeStruct((n,), np.float32)
+    fam = families.custom_ode(VDP, 2, 1, method="bs32")
+    text = pd.debug_msl(fam, grid=(n,), out_shape=(sh,) * 6, math_mode=pd.MathMode.SAFE)
+    assert "#define PD_MODE 0" in text and "#define PD_DIM 2" in text
+    assert VDP in text and 'extern "C" __global__' in text and "pd_ode_bs32" in text
+    src = families.source_kernel(SAXPY, "saxpy")
+    args = (np.ones(1, np.float32), np.zeros(n, np.float32), np.zeros(n, np.float32))
+    assert SAXPY in pd.debug_msl(src, *args, grid=(n,), out_shape=sh)
