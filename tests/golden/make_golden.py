@@ -73,7 +73,45 @@ def main():
     truth = oracle.kepler_rk4_f64(state64, dt=1e-3, steps=1000)
     np.savez_compressed(HERE / "df32.npz", lv_inputs=np.stack(lv_args), lv_x=dx, lv_y=dy, kepler_pairs=np.stack(pairs),
                         kepler_out=np.stack(kout), kepler_truth=truth)
+    reference_numpy_fixtures(lv_args)
     print("golden fixtures written to", HERE)
+
+
+def _reference_function(path: Path, name: str, namespace: dict):
+    """One function of a reference example, taken out of its module by name: the
+    examples import JAX and the Metal runtime at the top, which are not installed,
+    but these helpers are plain NumPy / SciPy."""
+    import ast
+
+    tree = ast.parse(path.read_text())
+    node = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == name)
+    code = compile(ast.Module(body=[node], type_ignores=[]), str(path), "exec")
+    exec(code, namespace)
+    return namespace[name]
+
+
+def reference_numpy_fixtures(lv_args):
+    """Outputs of the reference's own NumPy helpers, run here where its checkout
+    is: the float64 RK4 truth of examples/05_df32_precision.py:95-109 (its module
+    constants DT = 0.01, STEPS = 500, :24) and the closed-form call price of
+    examples/03_sde_montecarlo.py:73-76."""
+    from oracle.build import REFERENCE_ROOT
+
+    ex05 = REFERENCE_ROOT / "examples" / "05_df32_precision.py"
+    ex03 = REFERENCE_ROOT / "examples" / "03_sde_montecarlo.py"
+    if not ex05.exists() or not ex03.exists():
+        print("reference checkout not found: reference_numpy.npz left as it is")
+        return
+    from scipy.stats import norm
+
+    f64 = _reference_function(ex05, "float64_reference", {"np": np, "DT": 0.01, "STEPS": 500})
+    x64, y64 = f64(*lv_args)
+    bs = _reference_function(ex03, "black_scholes_call", {"np": np, "norm": norm})
+    cases = np.array([(100.0, 105.0, 1.0, 0.03, 0.2), (100.0, 100.0, 1.0, 0.05, 0.2), (80.0, 100.0, 0.5, 0.01, 0.35),
+                      (120.0, 100.0, 2.0, 0.0, 0.1)])
+    prices = np.array([bs(*c) for c in cases])
+    np.savez_compressed(HERE / "reference_numpy.npz", lv_inputs=np.stack(lv_args), lv_f64_x=x64, lv_f64_y=y64,
+                        bs_cases=cases, bs_prices=prices)
 
 
 if __name__ == "__main__":

@@ -325,3 +325,21 @@ def test_lv_df32_beats_float32_against_float64():
     dx, dy = oracle.lv_rk4_df32(*args, dt=0.01, steps=500)
     fx, fy = oracle.lv_rk4(*args, dt=0.01, steps=500)
     assert np.abs(dx - tx).max() < np.abs(fx - tx).max()  # examples/05_df32_precision.py:197
+
+
+def test_float64_truth_and_closed_form_price_match_the_references_own_numpy_code():
+    """tests/golden/reference_numpy.npz holds outputs of the reference's
+    `float64_reference` (examples/05_df32_precision.py:95-109) and
+    `black_scholes_call` (examples/03_sde_montecarlo.py:73-76), run from its
+    checkout by tests/golden/make_golden.py."""
+    g = np.load(GOLDEN / "reference_numpy.npz")
+    x, y = oracle.lv_rk4_f64(*g["lv_inputs"], dt=0.01, steps=500)
+    np.testing.assert_array_equal(x, g["lv_f64_x"])
+    np.testing.assert_array_equal(y, g["lv_f64_y"])
+    for case, price in zip(g["bs_cases"], g["bs_prices"]):
+        assert abs(oracle.black_scholes_call(*case) - price) <= 1e-12 * price
+    # the df32 kernel's reason to exist, against the reference's own truth (examples/05:197)
+    dx, dy = oracle.lv_rk4_df32(*g["lv_inputs"], dt=0.01, steps=500)
+    fx, fy = oracle.lv_rk4(*g["lv_inputs"], dt=0.01, steps=500)
+    assert np.max(np.abs(dx - g["lv_f64_x"])) < np.max(np.abs(fx - g["lv_f64_x"]))
+    assert np.max(np.abs(dy - g["lv_f64_y"])) < np.max(np.abs(fy - g["lv_f64_y"]))
