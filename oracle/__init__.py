@@ -52,6 +52,51 @@ def reference_lib() -> ctypes.CDLL | None:
     return _ref
 
 
+_ref_threefry = None
+
+
+def reference_threefry_lib() -> ctypes.CDLL | None:
+    """The Threefry block as the reference's emitter writes it, compiled for the
+    CPU, or None when it has not been built (needs a reference checkout)."""
+    global _ref_threefry
+    if _ref_threefry is None and _build.REF_THREEFRY_LIB.exists():
+        _ref_threefry = ctypes.CDLL(str(_build.REF_THREEFRY_LIB))
+    return _ref_threefry
+
+
+def reference_threefry(key, counters) -> np.ndarray:
+    """Blocks (key, counters[i]) -> (n, 2) uint32 through the reference's emitted statements."""
+    ref = reference_threefry_lib()
+    if ref is None:
+        raise RuntimeError("oracle/_ref/libthreefryref.so is not built")
+    key = _u32(key)
+    counters = _u32(counters).reshape(-1, 2)
+    out = np.empty_like(counters)
+    for i in range(counters.shape[0]):
+        ref.ref_threefry2x32(_p(key, _u32p), _p(counters[i].copy(), _u32p), _p(out[i:i + 1], _u32p))
+    return out
+
+
+def reference_random_bits(key, n: int) -> np.ndarray:
+    ref = reference_threefry_lib()
+    if ref is None:
+        raise RuntimeError("oracle/_ref/libthreefryref.so is not built")
+    key = _u32(key)
+    out = np.empty(n, np.uint32)
+    ref.ref_random_bits(_p(key, _u32p), ctypes.c_longlong(n), _p(out, _u32p))
+    return out
+
+
+def reference_fold_in(key, data) -> np.ndarray:
+    ref = reference_threefry_lib()
+    if ref is None:
+        raise RuntimeError("oracle/_ref/libthreefryref.so is not built")
+    key, data = _u32(key), _u32(np.atleast_1d(data))
+    out = np.empty((data.size, 2), np.uint32)
+    ref.ref_fold_in(_p(key, _u32p), _p(data, _u32p), ctypes.c_longlong(data.size), _p(out, _u32p))
+    return out
+
+
 def max_threads() -> int:
     return int(lib().orc_max_threads())
 

@@ -5,6 +5,12 @@
                              (tests/golden/rk4_lotka_volterra.metal, compiled as
                              C++ where it lies in the reference checkout), built
                              only when that checkout is present
+  oracle/_ref/libthreefryref.so   the Threefry-2x32-20 block as the reference's
+                             emitter writes it: the text-emitting helper
+                             `_emit_threefry2x32` (src/palladium/emit/rules.py:
+                             121-165) is run where it lies and the statements it
+                             emits are compiled as C; built only when the
+                             checkout is present
 
 Both use -O2 -ffp-contract=off (no fused multiply-add unless written as fmaf,
 no fast-math) so that each float operation rounds exactly once, in source order.
@@ -21,6 +27,7 @@ HERE = Path(__file__).resolve().parent
 ORACLE_LIB = HERE / "liboracle.so"
 REF_DIR = HERE / "_ref"
 REF_LIB = REF_DIR / "libmslref.so"
+REF_THREEFRY_LIB = REF_DIR / "libthreefryref.so"
 # The reference checkout: PALLADIUM_REFERENCE, else a directory named "reference" beside this repository.
 REFERENCE_ROOT = Path(os.environ.get("PALLADIUM_REFERENCE", str(HERE.parent.parent / "reference")))
 GOLDEN_RK4 = REFERENCE_ROOT / "tests" / "golden" / "rk4_lotka_volterra.metal"
@@ -62,6 +69,87 @@ def build_reference(force: bool = False) -> Path | None:
     return REF_LIB
 
 
+class _TextCursor:
+    """The two methods of the emitter's Cursor that `_emit_threefry2x32` uses
+    (it is documented as pure text emission: src/palladium/emit/rules.py:129-133)."""
+
+    def __init__(self) -> None:
+        self.lines: list[str] = []
+        self._count = 0
+
+    def fresh(self, prefix: str = "_t") -> str:
+        self._count += 1
+        return f"{prefix}{self._count}"
+
+    def emit(self, line: str) -> None:
+        self.lines.append(line)
+
+
+def reference_threefry_statements() -> tuple[list[str], str, str] | None:
+    """Runs the reference's `_emit_threefry2x32` on operands named k1, k2, c0, c1
+    and returns (emitted statements, name of output word 0, name of output word 1).
+    The function and its two rotation tables are taken out of rules.py by name:
+    the module itself imports JAX, which is not installed."""
+    import ast
+
+    rules = REFERENCE_ROOT / "src" / "palladium" / "emit" / "rules.py"
+    if not rules.exists():
+        return None
+    tree = ast.parse(rules.read_text())
+    wanted = []
+    for node in tree.body:
+        if isinstance(node, ast.Assign) and any(
+                isinstance(t, ast.Name) and t.id in ("_THREEFRY_ROT0", "_THREEFRY_ROT1") for t in node.targets):
+            wanted.append(node)
+        if isinstance(node, ast.FunctionDef) and node.name == "_emit_threefry2x32":
+            wanted.append(node)
+    if len(wanted) != 3:
+        raise RuntimeError("the reference's Threefry emitter was not found where expected in rules.py")
+    namespace: dict = {"Cursor": _TextCursor}
+    exec(compile(ast.Module(body=wanted, type_ignores=[]), str(rules), "exec"), namespace)
+    cursor = _TextCursor()
+    out0, out1 = namespace["_emit_threefry2x32"](cursor, "k1", "k2", "c0", "c1")
+    return cursor.lines, out0, out1
+
+
+def build_reference_threefry(force: bool = False) -> Path | None:
+    """Compile the Threefry block the reference's emitter writes, plus the two
+    compositions its rules make of it: random_bits = block(key, (0, flat index))
+    with the output words xor-ed (rules.py:168-185) and fold_in = block(key,
+    (0, data)) with both words as the new key (rules.py:188-201)."""
+    emitted = reference_threefry_statements()
+    if emitted is None:
+        return REF_THREEFRY_LIB if REF_THREEFRY_LIB.exists() else None
+    lines, out0, out1 = emitted
+    REF_DIR.mkdir(exist_ok=True)
+    src = REF_DIR / "threefry_ref.c"
+    body = "\n".join("    " + line for line in lines)
+    text = f"""/* generated by oracle/build.py from the reference's emitter; not source of this repository */
+typedef unsigned int uint;
+#define EXPORT __attribute__((visibility("default")))
+static void block(uint k1, uint k2, uint c0, uint c1, uint* o0, uint* o1) {{
+{body}
+    *o0 = {out0};
+    *o1 = {out1};
+}}
+EXPORT void ref_threefry2x32(const uint* key, const uint* ctr, uint* out) {{
+    block(key[0], key[1], ctr[0], ctr[1], &out[0], &out[1]);
+}}
+EXPORT void ref_random_bits(const uint* key, long long n, uint* out) {{
+    for (long long i = 0; i < n; ++i) {{ uint a, b; block(key[0], key[1], 0u, (uint)i, &a, &b); out[i] = a ^ b; }}
+}}
+EXPORT void ref_fold_in(const uint* key, const uint* data, long long n, uint* out) {{
+    for (long long i = 0; i < n; ++i) block(key[0], key[1], 0u, data[i], &out[2 * i], &out[2 * i + 1]);
+}}
+"""
+    if force or not src.exists() or src.read_text() != text or not REF_THREEFRY_LIB.exists():
+        src.write_text(text)
+        _run(["gcc", "-std=c11", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", str(src), "-o",
+              str(REF_THREEFRY_LIB)])
+    return REF_THREEFRY_LIB
+
+
 if __name__ == "__main__":
     print(build_oracle(force="-f" in sys.argv))
     print(build_reference(force="-f" in sys.argv))
+    print(build_reference_threefry(force="-f" in sys.argv))

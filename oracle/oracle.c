@@ -17,10 +17,18 @@
  *   rk4 lotka-volterra : pinned -- bit-identical to the reference's emitted
  *                        kernel tests/golden/rk4_lotka_volterra.metal compiled
  *                        as C++ (oracle/build.py builds it into oracle/_ref/).
- *   threefry / uniform / fold_in : PARITY UNPINNED -- the reference checks
- *                        these against a live jax.random and stores no vectors
- *                        (tests/test_10_random_bits.py:27-108); this follows the
- *                        emitter's specification src/palladium/emit/rules.py:121-201.
+ *   threefry block, random_bits, fold_in : pinned -- bit-identical to the
+ *                        statements the reference's emitter writes
+ *                        (`_emit_threefry2x32`, src/palladium/emit/rules.py:121-165,
+ *                        run where it lies and compiled as C by oracle/build.py
+ *                        into oracle/_ref/), with the counters of the random_bits
+ *                        and fold_in rules (:168-201).
+ *   uniform            : PARITY UNPINNED -- the reference checks it against a
+ *                        live jax.random and stores no vectors
+ *                        (tests/test_10_random_bits.py:42-54); the op chain is
+ *                        the one named at tests/test_10_random_bits.py:3-7.
+ *   float64 RK4 truth  : pinned -- bit-identical to the reference's NumPy
+ *                        `float64_reference` (examples/05_df32_precision.py:95-109).
  *   adaptive BS3(2), GBM, Gray-Scott : PARITY UNPINNED (no numeric fixtures in
  *                        the reference); restated from examples/02:69-171,
  *                        examples/03:97-119, examples/04:61-74.

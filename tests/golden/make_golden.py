@@ -74,6 +74,7 @@ def main():
     np.savez_compressed(HERE / "df32.npz", lv_inputs=np.stack(lv_args), lv_x=dx, lv_y=dy, kepler_pairs=np.stack(pairs),
                         kepler_out=np.stack(kout), kepler_truth=truth)
     reference_numpy_fixtures(lv_args)
+    reference_threefry_fixture()
     print("golden fixtures written to", HERE)
 
 
@@ -88,6 +89,31 @@ def _reference_function(path: Path, name: str, namespace: dict):
     code = compile(ast.Module(body=[node], type_ignores=[]), str(path), "exec")
     exec(code, namespace)
     return namespace[name]
+
+
+def reference_threefry_fixture():
+    """Outputs of the Threefry block exactly as the reference's emitter writes
+    it (`_emit_threefry2x32`, src/palladium/emit/rules.py:121-165, run from the
+    checkout and compiled as C by oracle/build.py), with the counter
+    constructions of its random_bits and fold_in rules (:168-201)."""
+    from oracle import build as oracle_build
+
+    if oracle_build.build_reference_threefry() is None:
+        print("reference checkout not found: threefry_reference.npz left as it is")
+        return
+    rng = np.random.default_rng(2024)
+    keys = rng.integers(0, 2 ** 32, (16, 2), dtype=np.uint64).astype(np.uint32)
+    keys[0] = (0, 0)
+    keys[1] = (0xFFFFFFFF, 0xFFFFFFFF)
+    counters = rng.integers(0, 2 ** 32, (16, 2), dtype=np.uint64).astype(np.uint32)
+    counters[0] = (0, 0)
+    counters[1] = (0xFFFFFFFF, 0xFFFFFFFF)
+    blocks = np.stack([oracle.reference_threefry(k, c)[0] for k, c in zip(keys, counters)])
+    data = np.array([0, 1, 2, 17, 251, 252, 0x7FFFFFFF, 0xFFFFFFFF], np.uint32)
+    bits = np.stack([oracle.reference_random_bits(k, 257) for k in keys[:4]])
+    folds = np.stack([oracle.reference_fold_in(k, data) for k in keys[:4]])
+    np.savez_compressed(HERE / "threefry_reference.npz", keys=keys, counters=counters, blocks=blocks, data=data,
+                        bits=bits, folds=folds)
 
 
 def reference_numpy_fixtures(lv_args):

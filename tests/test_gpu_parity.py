@@ -40,6 +40,17 @@ def test_fold_in_exact():
     np.testing.assert_array_equal(got, oracle.fold_in(key, data))
 
 
+def test_rng_kernels_against_the_references_emitted_threefry():
+    """The fixture holds outputs of the statements the reference's emitter writes
+    for Threefry (src/palladium/emit/rules.py:121-201), see tests/golden/make_golden.py."""
+    from pathlib import Path
+
+    g = np.load(Path(__file__).resolve().parent / "golden" / "threefry_reference.npz")
+    for key, bits, folds in zip(g["keys"], g["bits"], g["folds"]):
+        np.testing.assert_array_equal(H.threefry_solver("bits", bits.size)(key), bits)
+        np.testing.assert_array_equal(H.threefry_solver("fold_in", g["data"].size)(key, g["data"]), folds)
+
+
 def test_per_thread_independent_streams():
     # tests/test_10_random_bits.py:78-108 in the reference
     key = W.gbm_key(7)

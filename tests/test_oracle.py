@@ -343,3 +343,24 @@ def test_float64_truth_and_closed_form_price_match_the_references_own_numpy_code
     fx, fy = oracle.lv_rk4(*g["lv_inputs"], dt=0.01, steps=500)
     assert np.max(np.abs(dx - g["lv_f64_x"])) < np.max(np.abs(fx - g["lv_f64_x"]))
     assert np.max(np.abs(dy - g["lv_f64_y"])) < np.max(np.abs(fy - g["lv_f64_y"]))
+
+
+def test_threefry_matches_the_statements_the_references_emitter_writes():
+    """tests/golden/threefry_reference.npz was produced by running the reference's
+    `_emit_threefry2x32` (src/palladium/emit/rules.py:121-165) where it lies and
+    compiling the emitted statements as C (oracle/build.py); this pins the block,
+    the random_bits counter (0, flat index) with xor fold, and fold_in."""
+    g = load("threefry_reference")
+    for key, ctr, want in zip(g["keys"], g["counters"], g["blocks"]):
+        np.testing.assert_array_equal(oracle.threefry2x32(key, ctr), want)
+        a, b = oracle_np.threefry2x32(key[0], key[1], ctr[0], ctr[1])
+        assert (int(a), int(b)) == (int(want[0]), int(want[1]))
+    for key, bits, folds in zip(g["keys"], g["bits"], g["folds"]):
+        np.testing.assert_array_equal(oracle.random_bits(key, bits.size), bits)
+        np.testing.assert_array_equal(oracle.fold_in(key, g["data"]), folds)
+    if oracle.reference_threefry_lib() is not None:     # live, where the reference checkout is
+        rng = np.random.default_rng(99)
+        for _ in range(50):
+            key = rng.integers(0, 2 ** 32, 2, dtype=np.uint64).astype(np.uint32)
+            ctr = rng.integers(0, 2 ** 32, 2, dtype=np.uint64).astype(np.uint32)
+            np.testing.assert_array_equal(oracle.threefry2x32(key, ctr), oracle.reference_threefry(key, ctr)[0])
