@@ -97,6 +97,43 @@ def reference_fold_in(key, data) -> np.ndarray:
     return out
 
 
+_ref_gbm = None
+
+
+def reference_gbm_lib() -> ctypes.CDLL | None:
+    """The reference's hand-written `gbm_paths` MSL kernel compiled for the CPU,
+    or None when it has not been built (needs a reference checkout)."""
+    global _ref_gbm
+    if _ref_gbm is None and _build.REF_GBM_LIB.exists():
+        _ref_gbm = ctypes.CDLL(str(_build.REF_GBM_LIB))
+    return _ref_gbm
+
+
+def reference_gbm_paths(n: int, *, s0: float, strike: float, r: float, sigma: float, t: float, steps: int):
+    """Payoffs of the reference's own kernel, scalars formed as its driver forms
+    them (examples/03_sde_montecarlo.py:80-89)."""
+    ref = reference_gbm_lib()
+    if ref is None:
+        raise RuntimeError("oracle/_ref/libgbmref.so is not built")
+    dt = t / steps
+    drift_dt = np.float32((r - sigma**2 / 2) * dt)
+    vol_sqdt = np.float32(sigma * np.sqrt(dt))
+    payoff = np.empty(n, np.float32)
+    ref.ref_gbm_paths(_i64(n), ctypes.c_uint32(steps), ctypes.c_float(s0), ctypes.c_float(strike),
+                      ctypes.c_float(float(drift_dt)), ctypes.c_float(float(vol_sqdt)), _p(payoff, _f32p))
+    return payoff
+
+
+def reference_pcg_hash(values) -> np.ndarray:
+    ref = reference_gbm_lib()
+    if ref is None:
+        raise RuntimeError("oracle/_ref/libgbmref.so is not built")
+    values = _u32(values)
+    out = np.empty_like(values)
+    ref.ref_pcg_hash(_i64(values.size), _p(values, _u32p), _p(out, _u32p))
+    return out
+
+
 def max_threads() -> int:
     return int(lib().orc_max_threads())
 

@@ -5,6 +5,10 @@
                              (tests/golden/rk4_lotka_volterra.metal, compiled as
                              C++ where it lies in the reference checkout), built
                              only when that checkout is present
+  oracle/_ref/libgbmref.so   the reference's hand-written Monte Carlo kernel (the
+                             GBM_MSL string of examples/03_sde_montecarlo.py:34-70,
+                             taken out of the example where it lies), compiled as
+                             C++ through the same shim
   oracle/_ref/libthreefryref.so   the Threefry-2x32-20 block as the reference's
                              emitter writes it: the text-emitting helper
                              `_emit_threefry2x32` (src/palladium/emit/rules.py:
@@ -28,6 +32,7 @@ ORACLE_LIB = HERE / "liboracle.so"
 REF_DIR = HERE / "_ref"
 REF_LIB = REF_DIR / "libmslref.so"
 REF_THREEFRY_LIB = REF_DIR / "libthreefryref.so"
+REF_GBM_LIB = REF_DIR / "libgbmref.so"
 # The reference checkout: PALLADIUM_REFERENCE, else a directory named "reference" beside this repository.
 REFERENCE_ROOT = Path(os.environ.get("PALLADIUM_REFERENCE", str(HERE.parent.parent / "reference")))
 GOLDEN_RK4 = REFERENCE_ROOT / "tests" / "golden" / "rk4_lotka_volterra.metal"
@@ -67,6 +72,29 @@ def build_reference(force: bool = False) -> Path | None:
         _run(["g++", "-std=c++17", *CFLAGS, "-Wno-attributes", f"-I{HERE / 'msl_shim'}",
               f'-DPD_GOLDEN_RK4="{GOLDEN_RK4}"', str(src), "-o", str(REF_LIB)])
     return REF_LIB
+
+
+def build_reference_gbm(force: bool = False) -> Path | None:
+    """Compile the reference's hand-written `gbm_paths` MSL kernel for the CPU."""
+    import ast
+
+    example = REFERENCE_ROOT / "examples" / "03_sde_montecarlo.py"
+    if not example.exists():
+        return REF_GBM_LIB if REF_GBM_LIB.exists() else None
+    text = None
+    for node in ast.parse(example.read_text()).body:
+        if isinstance(node, ast.Assign) and any(isinstance(t, ast.Name) and t.id == "GBM_MSL" for t in node.targets):
+            text = ast.literal_eval(node.value)
+    if text is None:
+        raise RuntimeError("GBM_MSL was not found in the reference's Monte Carlo example")
+    REF_DIR.mkdir(exist_ok=True)
+    msl = REF_DIR / "gbm_paths.metal"   # generated from the reference; this directory is not committed
+    src = HERE / "msl_gbm_ref.cpp"
+    if force or not msl.exists() or msl.read_text() != text or _stale(REF_GBM_LIB, [src, HERE / "msl_shim" / "metal_stdlib"]):
+        msl.write_text(text)
+        _run(["g++", "-std=c++17", *CFLAGS, "-Wno-attributes", f"-I{HERE / 'msl_shim'}", f'-DPD_GBM_MSL="{msl}"',
+              str(src), "-o", str(REF_GBM_LIB)])
+    return REF_GBM_LIB
 
 
 class _TextCursor:
@@ -153,3 +181,4 @@ if __name__ == "__main__":
     print(build_oracle(force="-f" in sys.argv))
     print(build_reference(force="-f" in sys.argv))
     print(build_reference_threefry(force="-f" in sys.argv))
+    print(build_reference_gbm(force="-f" in sys.argv))

@@ -29,9 +29,12 @@
  *                        the one named at tests/test_10_random_bits.py:3-7.
  *   float64 RK4 truth  : pinned -- bit-identical to the reference's NumPy
  *                        `float64_reference` (examples/05_df32_precision.py:95-109).
- *   adaptive BS3(2), GBM, Gray-Scott : PARITY UNPINNED (no numeric fixtures in
- *                        the reference); restated from examples/02:69-171,
- *                        examples/03:97-119, examples/04:61-74.
+ *   GBM with pcg_hash  : pinned -- bit-identical to the reference's hand-written
+ *                        MSL kernel (GBM_MSL, examples/03_sde_montecarlo.py:34-70)
+ *                        compiled as C++ through oracle/msl_shim.
+ *   adaptive BS3(2), GBM with Threefry, Gray-Scott : PARITY UNPINNED (no
+ *                        numeric fixtures in the reference); restated from
+ *                        examples/02:69-171, examples/03:97-119, examples/04:61-74.
  *   df32 : PARITY UNPINNED -- the prelude (df_add/df_sub/df_mul) lives in the
  *                        external metal-runtime project, which is not in the
  *                        tree; textbook error-free transforms are used and

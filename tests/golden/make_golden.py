@@ -75,6 +75,7 @@ def main():
                         kepler_out=np.stack(kout), kepler_truth=truth)
     reference_numpy_fixtures(lv_args)
     reference_threefry_fixture()
+    reference_gbm_fixture()
     print("golden fixtures written to", HERE)
 
 
@@ -114,6 +115,25 @@ def reference_threefry_fixture():
     folds = np.stack([oracle.reference_fold_in(k, data) for k in keys[:4]])
     np.savez_compressed(HERE / "threefry_reference.npz", keys=keys, counters=counters, blocks=blocks, data=data,
                         bits=bits, folds=folds)
+
+
+def reference_gbm_fixture():
+    """Payoffs of the reference's hand-written Monte Carlo kernel `gbm_paths`
+    (the GBM_MSL text of examples/03_sde_montecarlo.py:34-70, compiled for the CPU
+    by oracle/build.py) at the example's own constants (:30-32) and at the
+    benchmark's, plus pcg_hash on its own."""
+    from oracle import build as oracle_build
+
+    if oracle_build.build_reference_gbm() is None:
+        print("reference checkout not found: gbm_pcg_reference.npz left as it is")
+        return
+    example = dict(s0=100.0, strike=105.0, r=0.03, sigma=0.2, t=1.0, steps=256)
+    bench = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=252)
+    values = np.concatenate([np.arange(4096, dtype=np.uint32),
+                             np.random.default_rng(7).integers(0, 2 ** 32, 4096, dtype=np.uint64).astype(np.uint32)])
+    np.savez_compressed(HERE / "gbm_pcg_reference.npz", example_payoff=oracle.reference_gbm_paths(4096, **example),
+                        bench_payoff=oracle.reference_gbm_paths(4096, **bench), hash_in=values,
+                        hash_out=oracle.reference_pcg_hash(values))
 
 
 def reference_numpy_fixtures(lv_args):

@@ -237,6 +237,25 @@ def test_gbm_pcg_matches_oracle(mode, rtol):
     np.testing.assert_allclose(got, want, rtol=rtol)
 
 
+def test_gbm_pcg_against_the_references_own_kernel():
+    """The fixture holds payoffs of the reference's hand-written `gbm_paths` MSL
+    kernel (examples/03_sde_montecarlo.py:34-70) compiled for the CPU, see
+    tests/golden/make_golden.py; the hash is compared exactly, the payoffs within
+    the difference between the C library's and CUDA's exp / log / cos."""
+    from pathlib import Path
+
+    g = np.load(Path(__file__).resolve().parent / "golden" / "gbm_pcg_reference.npz")
+    got = H.threefry_solver("pcg", 4096)(W.gbm_key(0))
+    np.testing.assert_array_equal(got, g["hash_out"][:4096])
+    example = dict(s0=100.0, strike=105.0, r=0.03, sigma=0.2, t=1.0, steps=256)
+    bench = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=252)
+    for cfg, want in ((example, g["example_payoff"]), (bench, g["bench_payoff"])):
+        got = H.gbm_pcg_solver(want.size, math_mode=SAFE, **cfg)()
+        # payoff = max(S - K, 0): an relative error of 1e-5 in S ~ 100 is 1e-3 absolute
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=2e-3)
+        assert np.array_equal(got > 0, want > 0) or np.sum((got > 0) != (want > 0)) <= 2
+
+
 def test_gbm_pcg_black_scholes_and_offsets(interpret_provider):
     # examples/03_sde_montecarlo.py:137-146 for the hand-written kernel
     n = 1 << 20

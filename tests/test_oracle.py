@@ -364,3 +364,18 @@ def test_threefry_matches_the_statements_the_references_emitter_writes():
             key = rng.integers(0, 2 ** 32, 2, dtype=np.uint64).astype(np.uint32)
             ctr = rng.integers(0, 2 ** 32, 2, dtype=np.uint64).astype(np.uint32)
             np.testing.assert_array_equal(oracle.threefry2x32(key, ctr), oracle.reference_threefry(key, ctr)[0])
+
+
+def test_gbm_pcg_equals_the_references_hand_written_kernel():
+    """tests/golden/gbm_pcg_reference.npz: payoffs of the reference's own `gbm_paths`
+    MSL kernel (examples/03_sde_montecarlo.py:34-70) compiled for the CPU through
+    oracle/msl_shim (oracle/build.py).  Same C library, same operation order:
+    the restatement is bit-identical."""
+    g = load("gbm_pcg_reference")
+    np.testing.assert_array_equal(oracle.pcg_hash(4096), g["hash_out"][:4096])
+    np.testing.assert_array_equal(oracle_np.pcg_hash(g["hash_in"]), g["hash_out"])
+    example = dict(s0=100.0, strike=105.0, r=0.03, sigma=0.2, t=1.0, steps=256)
+    bench = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=252)
+    for cfg, want in ((example, g["example_payoff"]), (bench, g["bench_payoff"])):
+        _, payoff = oracle.gbm_pcg(want.size, **cfg)
+        np.testing.assert_array_equal(payoff, want)
