@@ -134,6 +134,18 @@ def reference_pcg_hash(values) -> np.ndarray:
     return out
 
 
+def libm_f32(op: str, x, y=None) -> np.ndarray:
+    """powf / expf / logf / cosf / sqrtf of the C library, elementwise on float32."""
+    code = {"pow": 0, "exp": 1, "log": 2, "cos": 3, "sqrt": 4}[op]
+    x = np.ascontiguousarray(x, np.float32)
+    shape = x.shape
+    x = x.reshape(-1)
+    y = x if y is None else np.ascontiguousarray(np.broadcast_to(np.asarray(y, np.float32), shape)).reshape(-1)
+    out = np.empty_like(x)
+    lib().orc_libm_f32(ctypes.c_int(code), _i64(x.size), _p(x, _f32p), _p(y, _f32p), _p(out, _f32p))
+    return out.reshape(shape)
+
+
 def max_threads() -> int:
     return int(lib().orc_max_threads())
 

@@ -10,8 +10,9 @@
  *   - the adaptive Bogacki-Shampine 3(2) loop with PI controller of
  *     examples/02_adaptive_lockstep.py:69-171, run for the full max_steps
  *     iterations as the reference runs it (no early exit here).
- * Parity unpinned: the reference holds no numeric vectors for either loop on
- * systems other than its own examples.
+ * On the reference's own two systems these loops equal the pinned family
+ * oracles bit for bit; for other systems parity is unpinned (the reference has
+ * nothing to compare with).
  */
 #include <stdint.h>
 #include <math.h>

@@ -32,9 +32,12 @@
  *   GBM with pcg_hash  : pinned -- bit-identical to the reference's hand-written
  *                        MSL kernel (GBM_MSL, examples/03_sde_montecarlo.py:34-70)
  *                        compiled as C++ through oracle/msl_shim.
- *   adaptive BS3(2), GBM with Threefry, Gray-Scott : PARITY UNPINNED (no
- *                        numeric fixtures in the reference); restated from
- *                        examples/02:69-171, examples/03:97-119, examples/04:61-74.
+ *   adaptive BS3(2), GBM with Threefry, Gray-Scott : pinned -- bit-identical to
+ *                        the reference's own kernel functions (examples/02:69-171,
+ *                        examples/03:97-119, examples/04:61-74) executed on NumPy
+ *                        stand-ins for the jax / pl names they use
+ *                        (tests/golden/pallas_numpy.py, tests/golden/make_golden.py),
+ *                        with this C library's pow / exp / log / cos.
  *   df32 : PARITY UNPINNED -- the prelude (df_add/df_sub/df_mul) lives in the
  *                        external metal-runtime project, which is not in the
  *                        tree; textbook error-free transforms are used and
@@ -528,6 +531,22 @@ ORC_API void orc_kepler_rk4_f32(int64_t n, const float* in, float* out, double d
 /* the deterministic pow, exposed so tests can compare it with double pow */
 ORC_API void orc_pd_powf(int64_t n, const float* x, const float* y, float* out) {
     for (int64_t i = 0; i < n; ++i) out[i] = pd_powf(x[i], y[i]);
+}
+
+/* The C library's float functions on arrays, for the NumPy stand-in that runs the
+ * reference's Pallas kernel bodies (tests/golden/pallas_numpy.py): NumPy's own
+ * float32 loops for these functions round differently from the C library.
+ * op: 0 powf(x, y[i]), 1 expf, 2 logf, 3 cosf, 4 sqrtf. */
+ORC_API void orc_libm_f32(int op, int64_t n, const float* x, const float* y, float* out) {
+    for (int64_t i = 0; i < n; ++i) {
+        switch (op) {
+            case 0: out[i] = powf(x[i], y[i]); break;
+            case 1: out[i] = expf(x[i]); break;
+            case 2: out[i] = logf(x[i]); break;
+            case 3: out[i] = cosf(x[i]); break;
+            default: out[i] = sqrtf(x[i]); break;
+        }
+    }
 }
 
 ORC_API int orc_max_threads(void) {

@@ -20,6 +20,7 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent.parent))
+sys.path.insert(0, str(HERE))
 
 import oracle  # noqa: E402
 from palladium_b200 import workloads as W  # noqa: E402
@@ -76,6 +77,7 @@ def main():
     reference_numpy_fixtures(lv_args)
     reference_threefry_fixture()
     reference_gbm_fixture()
+    reference_kernel_fixture()
     print("golden fixtures written to", HERE)
 
 
@@ -134,6 +136,63 @@ def reference_gbm_fixture():
     np.savez_compressed(HERE / "gbm_pcg_reference.npz", example_payoff=oracle.reference_gbm_paths(4096, **example),
                         bench_payoff=oracle.reference_gbm_paths(4096, **bench), hash_in=values,
                         hash_out=oracle.reference_pcg_hash(values))
+
+
+def reference_kernel_fixture():
+    """Outputs of the reference's own Pallas kernel functions -- `lv_kernel`
+    (examples/01_ode_ensembles.py:72-91), `vdp_adaptive_kernel`
+    (examples/02_adaptive_lockstep.py:69-171), `pallas_gbm_kernel`
+    (examples/03_sde_montecarlo.py:97-119) and `gray_scott_kernel`
+    (examples/04_reaction_diffusion.py:61-74) -- taken out of the examples by name
+    and executed on NumPy stand-ins for the jax / pl names they use
+    (tests/golden/pallas_numpy.py), at the examples' own constants."""
+    from oracle.build import REFERENCE_ROOT
+
+    import pallas_numpy as PN
+
+    examples = REFERENCE_ROOT / "examples"
+    if not (examples / "02_adaptive_lockstep.py").exists():
+        print("reference checkout not found: reference_kernels.npz left as it is")
+        return
+    out = {}
+    # fixed-step RK4 (the example's DT and STEPS, examples/01:15-16)
+    n = 64
+    lv_in = W.lotka_volterra_ensemble(n)
+    kernel = PN.load_kernel(examples / "01_ode_ensembles.py", "lv_kernel", (n,), dict(DT=0.01, STEPS=500),
+                            outer="palladium_solver")
+    xo, yo = PN.Ref(PN.f32(np.zeros(n))), PN.Ref(PN.f32(np.zeros(n)))
+    kernel(*[PN.Ref(PN.f32(a)) for a in lv_in], xo, yo)
+    out.update(lv_in=np.stack(lv_in), lv_x=np.asarray(xo.array), lv_y=np.asarray(yo.array))
+    # adaptive BS3(2) (constants of examples/02:26-32)
+    n = 48
+    x0, v0, mu = W.van_der_pol_ensemble(n)
+    consts = dict(T1=10.0, DT0=0.01, MAX_STEPS=6000, RTOL=1e-5, ATOL=1e-7, ERROR_ORDER=3, SAFETY=0.9, FACTORMIN=0.2,
+                  FACTORMAX=10.0, pcoeff=0.4, icoeff=0.3)
+    kernel = PN.load_kernel(examples / "02_adaptive_lockstep.py", "vdp_adaptive_kernel", (n,), consts,
+                            outer="palladium_solver")
+    outs = [PN.Ref(PN.f32(np.zeros(n))) for _ in range(6)]
+    kernel(PN.Ref(PN.f32(x0)), PN.Ref(PN.f32(v0)), PN.Ref(PN.f32(mu)), *outs)
+    out.update(vdp_in=np.stack([x0, v0, mu]), vdp_out=np.stack([np.asarray(o.array) for o in outs]))
+    # Monte Carlo with in-kernel Threefry (constants of examples/03:30-32)
+    n = 512
+    key = W.gbm_key(0)
+    kernel = PN.load_kernel(examples / "03_sde_montecarlo.py", "pallas_gbm_kernel", (n,),
+                            dict(T=1.0, N_STEPS=256, R=0.03, SIGMA=0.2, S0=100.0, K=105.0))
+    payoff = PN.Ref(PN.f32(np.zeros(n)))
+    kernel(PN.Ref(key), payoff)
+    out.update(gbm_key=key, gbm_payoff=np.asarray(payoff.array))
+    # stencil (constants of examples/04:36)
+    n = 32
+    u0, v0g = W.gray_scott_initial_state(n, seed=11, patches=2, patch=8)
+    kernel = PN.load_kernel(examples / "04_reaction_diffusion.py", "gray_scott_kernel", (n, n),
+                            dict(SIZE=n, DU=0.16, DV=0.08, F=0.035, KK=0.065, DT=1.0))
+    u, v = PN.f32(u0.copy()), PN.f32(v0g.copy())
+    for _ in range(25):
+        uo, vo = PN.f32(np.zeros((n, n))), PN.f32(np.zeros((n, n)))
+        kernel(PN.Ref(u), PN.Ref(v), PN.Ref(uo), PN.Ref(vo))
+        u, v = uo, vo
+    out.update(gs_u0=u0, gs_v0=v0g, gs_u=np.asarray(u), gs_v=np.asarray(v))
+    np.savez_compressed(HERE / "reference_kernels.npz", **out)
 
 
 def reference_numpy_fixtures(lv_args):

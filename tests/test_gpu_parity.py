@@ -237,6 +237,37 @@ def test_gbm_pcg_matches_oracle(mode, rtol):
     np.testing.assert_allclose(got, want, rtol=rtol)
 
 
+def test_kernels_against_the_references_own_kernel_functions():
+    """tests/golden/reference_kernels.npz holds outputs of the reference's Pallas
+    kernel functions run on NumPy stand-ins (tests/golden/make_golden.py).  SAFE
+    kernels whose arithmetic is IEEE-exact match bit for bit; where a library
+    function is involved the bars are the reference's own (tests/test_08_adaptive.py:
+    174-189: t 1e-4, x and v 1e-3, counts within 20)."""
+    from pathlib import Path
+
+    g = np.load(Path(__file__).resolve().parent / "golden" / "reference_kernels.npz")
+    n = g["lv_x"].size
+    x, y = H.lv_solver(n, dt=0.01, steps=500, math_mode=SAFE)(*g["lv_in"])
+    np.testing.assert_array_equal(x, g["lv_x"])
+    np.testing.assert_array_equal(y, g["lv_y"])
+    rows = g["gs_u"].shape[0]
+    u, v = H.gs_solver(rows, rows, math_mode=SAFE, steps=25)(g["gs_u0"], g["gs_v0"])
+    np.testing.assert_array_equal(u, g["gs_u"])
+    np.testing.assert_array_equal(v, g["gs_v"])
+    cfg = dict(t1=10.0, rtol=1e-5, atol=1e-7, dt0=0.01, max_steps=6000)
+    for mode in (SAFE, RELAXED):
+        got = H.vdp_solver(g["vdp_in"].shape[1], outputs=6, math_mode=mode, **cfg)(*g["vdp_in"])
+        want = g["vdp_out"]
+        np.testing.assert_allclose(got[0], want[0], rtol=1e-4)
+        np.testing.assert_allclose(got[1], want[1], rtol=1e-3, atol=1e-3)
+        np.testing.assert_allclose(got[2], want[2], rtol=1e-3, atol=1e-3)
+        for k in (3, 4, 5):
+            np.testing.assert_allclose(got[k], want[k], atol=20)
+    payoff = H.gbm_solver(g["gbm_payoff"].size, math_mode=SAFE, s0=100.0, strike=105.0, r=0.03, sigma=0.2, t=1.0,
+                          steps=256)(g["gbm_key"])
+    np.testing.assert_allclose(payoff, g["gbm_payoff"], rtol=1e-5, atol=2e-3)
+
+
 def test_gbm_pcg_against_the_references_own_kernel():
     """The fixture holds payoffs of the reference's hand-written `gbm_paths` MSL
     kernel (examples/03_sde_montecarlo.py:34-70) compiled for the CPU, see

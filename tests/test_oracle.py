@@ -379,3 +379,29 @@ def test_gbm_pcg_equals_the_references_hand_written_kernel():
     for cfg, want in ((example, g["example_payoff"]), (bench, g["bench_payoff"])):
         _, payoff = oracle.gbm_pcg(want.size, **cfg)
         np.testing.assert_array_equal(payoff, want)
+
+
+def test_oracle_equals_the_references_own_kernel_functions():
+    """tests/golden/reference_kernels.npz: the reference's Pallas kernel functions
+    (examples/01:72-91, 02:69-171, 03:97-119, 04:61-74) executed on NumPy stand-ins
+    for the jax / pl names they use (tests/golden/pallas_numpy.py), with the C
+    library's pow / exp / log / cos.  The C oracle restates each of them and must
+    agree bit for bit: state, time, and all three counters of the adaptive loop."""
+    g = load("reference_kernels")
+    x, y = oracle.lv_rk4(*g["lv_in"], dt=0.01, steps=500)
+    np.testing.assert_array_equal(x, g["lv_x"])
+    np.testing.assert_array_equal(y, g["lv_y"])
+    got = oracle.vdp_bs32(*g["vdp_in"], pow="libm", t1=10.0, rtol=1e-5, atol=1e-7, dt0=0.01, max_steps=6000)
+    for have, want, name in zip(got, g["vdp_out"], ("t", "x", "v", "steps", "rejected", "real")):
+        np.testing.assert_array_equal(have, want, err_msg=name)
+    assert g["vdp_out"][4].max() > 0 and np.std(g["vdp_out"][5]) > 0      # rejections happen, counts differ
+    _, payoff = oracle.gbm(g["gbm_key"], g["gbm_payoff"].size, s0=100.0, strike=105.0, r=0.03, sigma=0.2, t=1.0,
+                           steps=256)
+    np.testing.assert_array_equal(payoff, g["gbm_payoff"])
+    assert 0.2 < np.mean(g["gbm_payoff"] > 0) < 0.6
+    u, v = oracle.gray_scott(g["gs_u0"], g["gs_v0"], steps=25)
+    np.testing.assert_array_equal(u, g["gs_u"])
+    np.testing.assert_array_equal(v, g["gs_v"])
+    nu, nv = oracle_np.gray_scott(g["gs_u0"], g["gs_v0"], steps=25)
+    np.testing.assert_array_equal(nu, g["gs_u"])
+    np.testing.assert_array_equal(nv, g["gs_v"])
