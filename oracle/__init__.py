@@ -134,6 +134,25 @@ def reference_pcg_hash(values) -> np.ndarray:
     return out
 
 
+_ref_df32 = None
+
+
+def reference_lv_rk4_df32(x0, y0, a, b, c, d, *, dt: float, steps: int):
+    """The reference's own df32 kernel text (examples/05_df32_precision.py:27-80)
+    on this oracle's df32 prelude; scalars as its driver passes them (:158)."""
+    global _ref_df32
+    if _ref_df32 is None:
+        if not _build.REF_DF32_LIB.exists():
+            raise RuntimeError("oracle/_ref/libdf32ref.so is not built")
+        _ref_df32 = ctypes.CDLL(str(_build.REF_DF32_LIB))
+    arrs = [_f32(v) for v in (x0, y0, a, b, c, d)]
+    n = arrs[0].size
+    xo, yo = np.empty(n, np.float32), np.empty(n, np.float32)
+    _ref_df32.ref_lv_rk4_df32(_i64(n), *[_p(v, _f32p) for v in arrs], _p(xo, _f32p), _p(yo, _f32p),
+                              ctypes.c_float(float(np.float32(dt))), ctypes.c_uint32(steps))
+    return xo, yo
+
+
 def libm_f32(op: str, x, y=None) -> np.ndarray:
     """powf / expf / logf / cosf / sqrtf of the C library, elementwise on float32."""
     code = {"pow": 0, "exp": 1, "log": 2, "cos": 3, "sqrt": 4}[op]

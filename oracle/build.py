@@ -9,6 +9,9 @@
                              GBM_MSL string of examples/03_sde_montecarlo.py:34-70,
                              taken out of the example where it lies), compiled as
                              C++ through the same shim
+  oracle/_ref/libdf32ref.so  the reference's hand-written df32 kernel (DF32_KERNEL of
+                             examples/05_df32_precision.py:27-80) on this oracle's
+                             restatement of the external df32 prelude
   oracle/_ref/libthreefryref.so   the Threefry-2x32-20 block as the reference's
                              emitter writes it: the text-emitting helper
                              `_emit_threefry2x32` (src/palladium/emit/rules.py:
@@ -33,6 +36,7 @@ REF_DIR = HERE / "_ref"
 REF_LIB = REF_DIR / "libmslref.so"
 REF_THREEFRY_LIB = REF_DIR / "libthreefryref.so"
 REF_GBM_LIB = REF_DIR / "libgbmref.so"
+REF_DF32_LIB = REF_DIR / "libdf32ref.so"
 # The reference checkout: PALLADIUM_REFERENCE, else a directory named "reference" beside this repository.
 REFERENCE_ROOT = Path(os.environ.get("PALLADIUM_REFERENCE", str(HERE.parent.parent / "reference")))
 GOLDEN_RK4 = REFERENCE_ROOT / "tests" / "golden" / "rk4_lotka_volterra.metal"
@@ -74,27 +78,43 @@ def build_reference(force: bool = False) -> Path | None:
     return REF_LIB
 
 
-def build_reference_gbm(force: bool = False) -> Path | None:
-    """Compile the reference's hand-written `gbm_paths` MSL kernel for the CPU."""
+def _module_string(example: Path, name: str) -> str:
+    """The string constant `name` of a reference example, without importing it."""
     import ast
 
-    example = REFERENCE_ROOT / "examples" / "03_sde_montecarlo.py"
-    if not example.exists():
-        return REF_GBM_LIB if REF_GBM_LIB.exists() else None
-    text = None
     for node in ast.parse(example.read_text()).body:
-        if isinstance(node, ast.Assign) and any(isinstance(t, ast.Name) and t.id == "GBM_MSL" for t in node.targets):
-            text = ast.literal_eval(node.value)
-    if text is None:
-        raise RuntimeError("GBM_MSL was not found in the reference's Monte Carlo example")
+        if isinstance(node, ast.Assign) and any(isinstance(t, ast.Name) and t.id == name for t in node.targets):
+            return ast.literal_eval(node.value)
+    raise RuntimeError(f"{name} was not found in {example.name}")
+
+
+def _build_msl_string(example: Path, name: str, msl_name: str, wrapper: str, define: str, lib: Path,
+                      force: bool) -> Path | None:
+    if not example.exists():
+        return lib if lib.exists() else None
+    text = _module_string(example, name)
     REF_DIR.mkdir(exist_ok=True)
-    msl = REF_DIR / "gbm_paths.metal"   # generated from the reference; this directory is not committed
-    src = HERE / "msl_gbm_ref.cpp"
-    if force or not msl.exists() or msl.read_text() != text or _stale(REF_GBM_LIB, [src, HERE / "msl_shim" / "metal_stdlib"]):
+    msl = REF_DIR / msl_name   # generated from the reference; this directory is not committed
+    src = HERE / wrapper
+    if force or not msl.exists() or msl.read_text() != text or _stale(
+            lib, [src, HERE / "msl_shim" / "metal_stdlib", HERE / "df32_ops.h"]):
         msl.write_text(text)
-        _run(["g++", "-std=c++17", *CFLAGS, "-Wno-attributes", f"-I{HERE / 'msl_shim'}", f'-DPD_GBM_MSL="{msl}"',
-              str(src), "-o", str(REF_GBM_LIB)])
-    return REF_GBM_LIB
+        _run(["g++", "-std=c++17", *CFLAGS, "-Wno-attributes", f"-I{HERE / 'msl_shim'}", f"-I{HERE}",
+              f'-D{define}="{msl}"', str(src), "-o", str(lib)])
+    return lib
+
+
+def build_reference_gbm(force: bool = False) -> Path | None:
+    """Compile the reference's hand-written `gbm_paths` MSL kernel for the CPU."""
+    return _build_msl_string(REFERENCE_ROOT / "examples" / "03_sde_montecarlo.py", "GBM_MSL", "gbm_paths.metal",
+                             "msl_gbm_ref.cpp", "PD_GBM_MSL", REF_GBM_LIB, force)
+
+
+def build_reference_df32(force: bool = False) -> Path | None:
+    """Compile the reference's hand-written `lv_rk4_df32` MSL kernel for the CPU
+    (on this oracle's restatement of the df32 prelude it expects)."""
+    return _build_msl_string(REFERENCE_ROOT / "examples" / "05_df32_precision.py", "DF32_KERNEL",
+                             "lv_rk4_df32.metal", "msl_df32_ref.cpp", "PD_DF32_MSL", REF_DF32_LIB, force)
 
 
 class _TextCursor:
@@ -182,3 +202,4 @@ if __name__ == "__main__":
     print(build_reference(force="-f" in sys.argv))
     print(build_reference_threefry(force="-f" in sys.argv))
     print(build_reference_gbm(force="-f" in sys.argv))
+    print(build_reference_df32(force="-f" in sys.argv))

@@ -38,10 +38,13 @@
  *                        stand-ins for the jax / pl names they use
  *                        (tests/golden/pallas_numpy.py, tests/golden/make_golden.py),
  *                        with this C library's pow / exp / log / cos.
- *   df32 : PARITY UNPINNED -- the prelude (df_add/df_sub/df_mul) lives in the
- *                        external metal-runtime project, which is not in the
- *                        tree; textbook error-free transforms are used and
- *                        checked for exactness with rational arithmetic.
+ *   df32 : kernel structure pinned (bit-identical to the reference's DF32_KERNEL
+ *                        text, examples/05_df32_precision.py:27-80, compiled on
+ *                        df32_ops.h); arithmetic PARITY UNPINNED -- the prelude
+ *                        (df_add/df_sub/df_mul) lives in the external
+ *                        metal-runtime project, which is not in the tree;
+ *                        textbook error-free transforms are used and checked for
+ *                        exactness with rational arithmetic.
  */
 #include <math.h>
 #include <stdint.h>
@@ -333,60 +336,7 @@ ORC_API int orc_gray_scott(int64_t rows, int64_t cols, const float* u, const flo
 /* ------------------------------------------------------------------------- */
 /* df32 arithmetic, restated from the textbook definitions.                    */
 /* ------------------------------------------------------------------------- */
-typedef struct { float hi, lo; } df;
-
-static inline df two_sum(float a, float b) {          /* Knuth */
-    df r; r.hi = a + b;
-    float bv = r.hi - a;
-    float av = r.hi - bv;
-    r.lo = (a - av) + (b - bv);
-    return r;
-}
-static inline df quick_two_sum(float a, float b) {    /* Dekker, |a| >= |b| */
-    df r; r.hi = a + b; r.lo = b - (r.hi - a); return r;
-}
-static inline df two_prod(float a, float b) {         /* FMA */
-    df r; r.hi = a * b; r.lo = fmaf(a, b, -r.hi); return r;
-}
-static inline df dfc(float a) { df r; r.hi = a; r.lo = 0.0f; return r; }
-static inline df df_add(df a, df b) {
-    df s = two_sum(a.hi, b.hi), t = two_sum(a.lo, b.lo);
-    s.lo = s.lo + t.hi;
-    s = quick_two_sum(s.hi, s.lo);
-    s.lo = s.lo + t.lo;
-    return quick_two_sum(s.hi, s.lo);
-}
-static inline df df_neg(df a) { df r; r.hi = -a.hi; r.lo = -a.lo; return r; }
-static inline df df_sub(df a, df b) { return df_add(a, df_neg(b)); }
-static inline df df_mul(df a, df b) {
-    df p = two_prod(a.hi, b.hi);
-    p.lo = fmaf(a.hi, b.lo, p.lo);
-    p.lo = fmaf(a.lo, b.hi, p.lo);
-    return quick_two_sum(p.hi, p.lo);
-}
-static inline df df_div(df a, df b) {
-    float q1 = a.hi / b.hi;
-    df r = df_sub(a, df_mul(dfc(q1), b));
-    float q2 = r.hi / b.hi;
-    r = df_sub(r, df_mul(dfc(q2), b));
-    float q3 = r.hi / b.hi;
-    return df_add(quick_two_sum(q1, q2), dfc(q3));
-}
-/* 1 / b: q = 1 / b.hi, e = 1 - b q formed exactly, result q + q e */
-static inline df df_recip(df b) {
-    float q = 1.0f / b.hi;
-    df p = two_prod(b.hi, q);
-    p.lo = fmaf(b.lo, q, p.lo);
-    float e = (1.0f - p.hi) - p.lo;
-    return quick_two_sum(q, q * e);
-}
-static inline df df_twice(df a) { df r; r.hi = a.hi + a.hi; r.lo = a.lo + a.lo; return r; }
-static inline df df_sqrt(df a) {
-    float s = sqrtf(a.hi);
-    if (s == 0.0f) return dfc(0.0f);
-    df d = df_sub(a, two_prod(s, s));
-    return quick_two_sum(s, d.hi / (s + s));
-}
+#include "df32_ops.h"
 
 /* elementwise df32 primitives, for exactness tests: op 0 add, 1 sub, 2 mul, 3 div, 4 sqrt(a) */
 ORC_API void orc_df_op(int op, int64_t n, const float* ah, const float* al, const float* bh, const float* bl,

@@ -78,6 +78,7 @@ def main():
     reference_threefry_fixture()
     reference_gbm_fixture()
     reference_kernel_fixture()
+    reference_df32_fixture(lv_args)
     print("golden fixtures written to", HERE)
 
 
@@ -193,6 +194,20 @@ def reference_kernel_fixture():
         u, v = uo, vo
     out.update(gs_u0=u0, gs_v0=v0g, gs_u=np.asarray(u), gs_v=np.asarray(v))
     np.savez_compressed(HERE / "reference_kernels.npz", **out)
+
+
+def reference_df32_fixture(lv_args):
+    """Outputs of the reference's hand-written df32 kernel text (DF32_KERNEL,
+    examples/05_df32_precision.py:27-80) compiled for the CPU on the oracle's
+    restatement of the external df32 prelude (oracle/build.py): pins the kernel's
+    structure, not the prelude's arithmetic."""
+    from oracle import build as oracle_build
+
+    if oracle_build.build_reference_df32() is None:
+        print("reference checkout not found: df32_reference.npz left as it is")
+        return
+    x, y = oracle.reference_lv_rk4_df32(*lv_args, dt=0.01, steps=500)
+    np.savez_compressed(HERE / "df32_reference.npz", lv_inputs=np.stack(lv_args), x=x, y=y)
 
 
 def reference_numpy_fixtures(lv_args):

@@ -268,6 +268,18 @@ def test_kernels_against_the_references_own_kernel_functions():
     np.testing.assert_allclose(payoff, g["gbm_payoff"], rtol=1e-5, atol=2e-3)
 
 
+def test_df32_kernel_against_the_references_kernel_text():
+    """The fixture: the reference's DF32_KERNEL text compiled for the CPU on the
+    oracle's df32 prelude (tests/golden/make_golden.py)."""
+    from pathlib import Path
+
+    g = np.load(Path(__file__).resolve().parent / "golden" / "df32_reference.npz")
+    n = g["x"].size
+    x, y = H.lv_solver(n, dt=0.01, steps=500, df32=True, math_mode=SAFE)(*g["lv_inputs"])
+    np.testing.assert_array_equal(x, g["x"])
+    np.testing.assert_array_equal(y, g["y"])
+
+
 def test_gbm_pcg_against_the_references_own_kernel():
     """The fixture holds payoffs of the reference's hand-written `gbm_paths` MSL
     kernel (examples/03_sde_montecarlo.py:34-70) compiled for the CPU, see

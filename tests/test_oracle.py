@@ -405,3 +405,14 @@ def test_oracle_equals_the_references_own_kernel_functions():
     nu, nv = oracle_np.gray_scott(g["gs_u0"], g["gs_v0"], steps=25)
     np.testing.assert_array_equal(nu, g["gs_u"])
     np.testing.assert_array_equal(nv, g["gs_v"])
+
+
+def test_df32_kernel_structure_equals_the_references_kernel_text():
+    """tests/golden/df32_reference.npz: the reference's DF32_KERNEL text
+    (examples/05_df32_precision.py:27-80) compiled for the CPU on the oracle's df32
+    prelude.  Operation order, constants (0.5f * dt, dt / 6.0f in float32) and the
+    RK4 combination are the reference's; the prelude arithmetic is restated."""
+    g = load("df32_reference")
+    x, y = oracle.lv_rk4_df32(*g["lv_inputs"], dt=0.01, steps=500)
+    np.testing.assert_array_equal(x, g["x"])
+    np.testing.assert_array_equal(y, g["y"])
