@@ -206,6 +206,38 @@ def bench_lv_df32(n: int, steps: int, warmup: int = 1, iters: int = 3, fma_peak:
     return res
 
 
+# The Lotka-Volterra right-hand side as a caller would hand it to `custom_ode`:
+# in the reference's expression order, and factored so that each line is one
+# multiply by a fused multiply-add.
+CUSTOM_LV_RHS = "dy[0] = p[0]*y[0] - (p[1]*y[0])*y[1];\ndy[1] = (p[2]*y[0])*y[1] - p[3]*y[1];"
+CUSTOM_LV_RHS_FACTORED = "dy[0] = y[0]*fmaf(-p[1], y[1], p[0]);\ndy[1] = y[1]*fmaf(p[2], y[0], -p[3]);"
+
+
+def bench_custom_ode(n: int, steps: int, math_mode: str = "fast", rhs: str = CUSTOM_LV_RHS_FACTORED, warmup: int = 2,
+                     iters: int = 5, fma_peak: float | None = None) -> dict:
+    """The run-time compiled RK4 kernel on the Lotka-Volterra system, beside the
+    hand-written family on the same inputs."""
+    import torch
+
+    from . import cuda_call_jit, families
+    from . import workloads as W
+
+    out_shape = (_shaped((n,)), _shaped((n,)))
+    custom = cuda_call_jit(families.custom_ode(rhs, 2, 4, dt=0.01, steps=steps), grid=(n,), out_shape=out_shape,
+                           math_mode=math_mode)
+    family = cuda_call_jit(families.lv_rk4(0.01, steps), grid=(n,), out_shape=out_shape, math_mode=math_mode)
+    dev = [torch.from_numpy(a).cuda() for a in W.lotka_volterra_ensemble(n)]
+    ms = _time(lambda: custom(*dev), warmup, iters)
+    ms_family = _time(lambda: family(*dev), warmup, iters)
+    ts = float(n) * steps
+    res = {"workload": "run-time compiled RK4 (custom_ode) on Lotka-Volterra", "trajectories": n,
+           "steps_per_call": steps, "math_mode": math_mode, "ms": ms, "trajectory_steps_per_s": ts / (ms * 1e-3),
+           "hand_written_family_ms": ms_family, "ratio_to_family": ms / ms_family}
+    if fma_peak:
+        res["frac_of_fp32_peak"] = res["trajectory_steps_per_s"] * 58 / fma_peak
+    return res
+
+
 def quick_summary() -> dict:
     """Each family once, at a reduced size that finishes in a few seconds."""
     from . import _native
@@ -220,6 +252,7 @@ def quick_summary() -> dict:
     out["gray_scott"] = bench_gray_scott(8192, 40, "fast")
     out["kepler_df32"] = bench_kepler(1 << 20, 100, fma_peak=fma_peak)
     out["lv_df32"] = bench_lv_df32(1 << 20, 100, fma_peak=fma_peak)
+    out["custom_ode_lv"] = bench_custom_ode(1 << 22, 1000, "fast", fma_peak=fma_peak)
     return out
 
 
@@ -352,6 +385,17 @@ def run(args, rank: int, local_rank: int, world: int, barrier, max_over_ranks) -
         line.update({"metric": "df32_trajectory_steps_per_s", "value": value, "unit": "trajectory-steps/s",
                      "ms_per_step": ms, "scaling": "weak", "gpu_launches": steps, "config": {"workload": "kepler_df32", **r},
                      "roofline": {"bound": "fp32_fma", "achieved": r["trajectory_steps_per_s"] * DF32_KEPLER_FLOPS / 1e12,
+                                  "peak": fma_peak / 1e12, "unit": "TFLOP/s", "frac": r.get("frac_of_fp32_peak"),
+                                  "traffic": None}})
+    elif name == "custom_ode":
+        n = args.n or (1 << 22)
+        r = bench_custom_ode(n, 1000, args.math_mode, warmup=warmup, iters=steps, fma_peak=fma_peak)
+        ms = max_over_ranks(r["ms"])
+        value = float(n) * world * 1000 / (ms * 1e-3)
+        line.update({"metric": "rk4_ensemble_trajectory_steps_per_s", "value": value, "unit": "trajectory-steps/s",
+                     "ms_per_step": ms, "scaling": "weak", "gpu_launches": steps,
+                     "config": {"workload": "custom_ode_lotka_volterra", **r},
+                     "roofline": {"bound": "fp32_fma", "achieved": r["trajectory_steps_per_s"] * 58 / 1e12,
                                   "peak": fma_peak / 1e12, "unit": "TFLOP/s", "frac": r.get("frac_of_fp32_peak"),
                                   "traffic": None}})
     elif name == "full":
