@@ -205,6 +205,52 @@ typedef struct pd_launch_info {
     int32_t blocks_per_sm;     /* occupancy; -1 when no CUDA device is present */
 } pd_launch_info;
 
+/* ---- row slabs on several GPUs: the halo exchange from inside the kernel ----
+ * The reference has no multi-device code; this is the multi-GPU form of its
+ * stepping loop (examples/04_reaction_diffusion.py:92-109).  A slab call
+ * (pd_launch, PD_FAMILY_GRAY_SCOTT, halo > 0) leaves rows [halo, halo + rows)
+ * valid; the neighbours above and below need this slab's first and last `halo`
+ * owned rows in their ghost rows before their next call.  pd_gray_scott_slab_push
+ * is the same call with the neighbours' OUTPUT fields given as peer device
+ * pointers (mapped with pd_peer_open below): the final launch of the call stores
+ * the boundary rows to its own output and, from the same registers, to the
+ * neighbours' ghost rows, plain stores that travel over NVLink.  Nothing waits
+ * inside the kernel: the caller orders "every rank's call has finished" before
+ * any rank's next call (one barrier on the host or a one-element all-reduce on
+ * the stream), and alternates two output sets so that a neighbour never reads
+ * the set being pushed into.
+ *   up_*:   fields of the slab that owns the rows above this one; this slab's rows
+ *           [halo, 2*halo) land in its rows [halo + up_rows, 2*halo + up_rows).
+ *   down_*: fields of the slab below; this slab's rows [rows, rows + halo) land
+ *           in its rows [0, halo).
+ * Requires rows >= halo.  On one rank (periodic wrap onto itself) the neighbours
+ * are the call's own outputs. */
+typedef struct pd_gs_neighbours {
+    void* up_u;
+    void* up_v;
+    int64_t up_rows;     /* owned rows of the upper neighbour (its fields have up_rows + 2*halo rows) */
+    void* down_u;
+    void* down_v;
+    int64_t down_rows;
+} pd_gs_neighbours;
+
+PD_API int pd_gray_scott_slab_push(const pd_gray_scott_params* params, int math_mode,
+                                   const void* u, const void* v, void* uo, void* vo,
+                                   const pd_gs_neighbours* neighbours,
+                                   void* workspace, size_t workspace_bytes,
+                                   void* cuda_stream, char* err, size_t err_cap);
+
+/* Device memory that another process on the same node can map (CUDA IPC):
+ * pd_peer_alloc returns a whole allocation, pd_peer_export its 64-byte handle,
+ * pd_peer_open maps a handle received from another rank (peer access is enabled
+ * on first use), pd_peer_close / pd_peer_free release them. */
+#define PD_PEER_HANDLE_BYTES 64
+PD_API int pd_peer_alloc(size_t bytes, void** ptr, char* err, size_t err_cap);
+PD_API int pd_peer_export(void* ptr, unsigned char handle[PD_PEER_HANDLE_BYTES], char* err, size_t err_cap);
+PD_API int pd_peer_open(const unsigned char handle[PD_PEER_HANDLE_BYTES], void** ptr, char* err, size_t err_cap);
+PD_API int pd_peer_close(void* ptr, char* err, size_t err_cap);
+PD_API int pd_peer_free(void* ptr, char* err, size_t err_cap);
+
 /* Compile a PD_FAMILY_CUSTOM_ODE right-hand side for sm_100a without loading or
  * launching it: needs NVRTC but no CUDA device, so a host can reject a faulty
  * right-hand side where it is defined (the reference raises at trace time,

@@ -52,6 +52,12 @@ EXPORTED_SYMBOLS = (
     "pd_custom_ode_check",
     "pd_source_kernel_check",
     "pd_custom_ode_source",
+    "pd_gray_scott_slab_push",
+    "pd_peer_alloc",
+    "pd_peer_export",
+    "pd_peer_open",
+    "pd_peer_close",
+    "pd_peer_free",
 )
 
 FAMILY_IDS = {
@@ -114,6 +120,14 @@ class SourceKernelParams(ctypes.Structure):
     _fields_ = [("cuda_source", ctypes.c_char_p), ("function_name", ctypes.c_char_p)]
 
 
+class GsNeighbours(ctypes.Structure):
+    _fields_ = [("up_u", ctypes.c_void_p), ("up_v", ctypes.c_void_p), ("up_rows", _i64),
+                ("down_u", ctypes.c_void_p), ("down_v", ctypes.c_void_p), ("down_rows", _i64)]
+
+
+PEER_HANDLE_BYTES = 64
+
+
 class LaunchInfo(ctypes.Structure):
     _fields_ = [("kernel_name", ctypes.c_char * 64), ("cuda_grid", _i64 * 3), ("cuda_block", _i64 * 3),
                 ("items_per_thread", _i64), ("launches", _i64), ("scratch_bytes", _i64),
@@ -160,6 +174,19 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pd_last_kernel_ms.argtypes = []
     lib.pd_gray_scott_static.restype = ci
     lib.pd_gray_scott_static.argtypes = [ctypes.POINTER(GrayScottParams), ci, vp, vp, vp, vp, vp, cp, sz]
+    lib.pd_gray_scott_slab_push.restype = ci
+    lib.pd_gray_scott_slab_push.argtypes = [ctypes.POINTER(GrayScottParams), ci, vp, vp, vp, vp,
+                                            ctypes.POINTER(GsNeighbours), vp, sz, vp, cp, sz]
+    lib.pd_peer_alloc.restype = ci
+    lib.pd_peer_alloc.argtypes = [sz, vpp, cp, sz]
+    lib.pd_peer_export.restype = ci
+    lib.pd_peer_export.argtypes = [vp, cp, cp, sz]
+    lib.pd_peer_open.restype = ci
+    lib.pd_peer_open.argtypes = [cp, vpp, cp, sz]
+    lib.pd_peer_close.restype = ci
+    lib.pd_peer_close.argtypes = [vp, cp, sz]
+    lib.pd_peer_free.restype = ci
+    lib.pd_peer_free.argtypes = [vp, cp, sz]
     lib.pd_custom_ode_check.restype = ci
     lib.pd_custom_ode_check.argtypes = [ctypes.POINTER(CustomOdeParams), sz, ci, cp, sz, cp, sz]
     lib.pd_custom_ode_source.restype = ci
@@ -353,3 +380,56 @@ def custom_ode_source(params: CustomOdeParams, math_mode: int = 2) -> str:
     if rc:
         _raise(rc, err.value)
     return out.value.decode("utf-8", "replace")
+
+
+def gray_scott_slab_push(params: GrayScottParams, math_mode: int, u: int, v: int, uo: int, vo: int,
+                         neighbours: GsNeighbours, stream: int = 0) -> None:
+    """pd_gray_scott_slab_push on device pointers: a slab call whose final launch
+    also stores the boundary rows into the neighbours' ghost rows (peer memory)."""
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_gray_scott_slab_push(ctypes.byref(params), math_mode, u, v, uo, vo, ctypes.byref(neighbours),
+                                           None, 0, stream or None, err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+
+
+def peer_alloc(nbytes: int) -> int:
+    out = ctypes.c_void_p()
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_peer_alloc(int(nbytes), ctypes.byref(out), err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    return int(out.value)
+
+
+def peer_export(ptr: int) -> bytes:
+    handle = ctypes.create_string_buffer(PEER_HANDLE_BYTES)
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_peer_export(ptr, handle, err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    return handle.raw
+
+
+def peer_open(handle: bytes) -> int:
+    out = ctypes.c_void_p()
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_peer_open(ctypes.create_string_buffer(handle, PEER_HANDLE_BYTES), ctypes.byref(out), err,
+                                _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    return int(out.value)
+
+
+def peer_close(ptr: int) -> None:
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_peer_close(ptr, err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+
+
+def peer_free(ptr: int) -> None:
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_peer_free(ptr, err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)

@@ -518,7 +518,7 @@ void split_df32(double v, float* hi, float* lo) {
 int launch_impl(int family, const void* params, size_t params_bytes, int math_mode, const int64_t grid[3],
                 const int64_t block[3], int n_in, const void* const* in, const size_t* in_bytes, int n_out,
                 void* const* out, const size_t* out_bytes, void* workspace, size_t workspace_bytes,
-                cudaStream_t st, char* err, size_t err_cap) {
+                cudaStream_t st, char* err, size_t err_cap, const pd_gs_neighbours* neighbours = nullptr) {
     DeviceFacts dev = device_facts();
     if (!dev.present)
         return fail(PD_ERR_CUDA, err, err_cap,
@@ -645,7 +645,7 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             const pd_gray_scott_params* p = static_cast<const pd_gray_scott_params*>(params);
             const int rows_alloc = (int)(p->rows + 2 * p->halo);
             const size_t field_bytes = (size_t)rows_alloc * (size_t)p->cols * sizeof(float);
-            PdGsArgs a;
+            PdGsArgs a = {};
             a.rows_alloc = rows_alloc; a.cols = (int)p->cols;
             a.periodic_rows = p->halo == 0 ? 1 : 0;
             a.du = (float)p->du; a.dv = (float)p->dv; a.f = (float)p->f; a.fk = (float)(p->f + p->k);
@@ -675,7 +675,19 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
                 if (p->halo == 0) { a.row_lo = 0; a.row_hi = rows_alloc; }
                 else { a.row_lo = (int)(done + k); a.row_hi = rows_alloc - (int)(done + k); }
                 const int variant = k >= 2 ? tb_base + k : (plan.variant >= 12 ? 1 : plan.variant);
+                const bool last = done + k >= p->steps;
+                if (last && neighbours) {
+                    // The final launch also feeds the neighbours' ghost rows: from its own
+                    // stores when it is a temporally blocked launch, else by a copy kernel.
+                    const int h = (int)p->halo, rows = (int)p->rows;
+                    a.top_lo = h; a.top_hi = 2 * h; a.up_shift = (int)neighbours->up_rows;
+                    a.bot_lo = rows; a.bot_hi = rows + h; a.dn_shift = -rows;
+                    a.up_u = (float*)neighbours->up_u; a.up_v = (float*)neighbours->up_v;
+                    a.dn_u = (float*)neighbours->down_u; a.dn_v = (float*)neighbours->down_v;
+                    a.push = k >= 2 ? 1 : 0;
+                }
                 PD_CUDA_TRY(mt->gray_scott(a, variant, st));
+                if (last && neighbours && !a.push) PD_CUDA_TRY(mt->gray_scott(a, -1, st));
                 src_u = a.uo; src_v = a.vo;
                 to_out = !to_out;
                 done += k;
@@ -792,6 +804,68 @@ int pd_launch(int family, const void* params, size_t params_bytes, int math_mode
               void* cuda_stream, char* err, size_t err_cap) {
     return launch_impl(family, params, params_bytes, math_mode, grid, block, n_in, in, in_bytes, n_out, out,
                        out_bytes, workspace, workspace_bytes, (cudaStream_t)cuda_stream, err, err_cap);
+}
+
+int pd_gray_scott_slab_push(const pd_gray_scott_params* params, int math_mode, const void* u, const void* v,
+                            void* uo, void* vo, const pd_gs_neighbours* nb, void* workspace, size_t workspace_bytes,
+                            void* cuda_stream, char* err, size_t err_cap) {
+    if (!params || !nb) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "params and neighbours must not be NULL");
+    if (params->halo <= 0)
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott push: the call needs a slab (halo > 0)");
+    if (params->steps <= 0)
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott push: steps must be positive");
+    if (params->rows < params->halo)
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                    "gray_scott push: a slab of %lld rows cannot serve %lld halo rows", (long long)params->rows,
+                    (long long)params->halo);
+    if (!nb->up_u || !nb->up_v || !nb->down_u || !nb->down_v)
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott push: neighbour pointers must not be NULL");
+    if (nb->up_rows < params->halo || nb->down_rows < params->halo)
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott push: neighbour slabs are smaller than the halo");
+    if (!aligned(nb->up_u, 16) || !aligned(nb->up_v, 16) || !aligned(nb->down_u, 16) || !aligned(nb->down_v, 16))
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott push: neighbour fields must be 16-byte aligned");
+    const int64_t grid[3] = {params->rows, params->cols, 1};
+    const size_t bytes = (size_t)(params->rows + 2 * params->halo) * (size_t)params->cols * sizeof(float);
+    const void* in[2] = {u, v};
+    void* out[2] = {uo, vo};
+    const size_t sizes[2] = {bytes, bytes};
+    return launch_impl(PD_FAMILY_GRAY_SCOTT, params, sizeof(*params), math_mode, grid, nullptr, 2, in, sizes, 2, out,
+                       sizes, workspace, workspace_bytes, (cudaStream_t)cuda_stream, err, err_cap, nb);
+}
+
+int pd_peer_alloc(size_t bytes, void** ptr, char* err, size_t err_cap) {
+    if (!ptr || bytes == 0) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "pd_peer_alloc: bad arguments");
+    PD_CUDA_TRY(cudaMalloc(ptr, bytes));
+    return PD_OK;
+}
+
+int pd_peer_export(void* ptr, unsigned char handle[PD_PEER_HANDLE_BYTES], char* err, size_t err_cap) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == PD_PEER_HANDLE_BYTES, "IPC handle size");
+    if (!ptr || !handle) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "pd_peer_export: bad arguments");
+    cudaIpcMemHandle_t h;
+    PD_CUDA_TRY(cudaIpcGetMemHandle(&h, ptr));
+    memcpy(handle, &h, sizeof h);
+    return PD_OK;
+}
+
+int pd_peer_open(const unsigned char handle[PD_PEER_HANDLE_BYTES], void** ptr, char* err, size_t err_cap) {
+    if (!ptr || !handle) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "pd_peer_open: bad arguments");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    PD_CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return PD_OK;
+}
+
+int pd_peer_close(void* ptr, char* err, size_t err_cap) {
+    if (!ptr) return PD_OK;
+    PD_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+    return PD_OK;
+}
+
+int pd_peer_free(void* ptr, char* err, size_t err_cap) {
+    if (!ptr) return PD_OK;
+    PD_CUDA_TRY(cudaFree(ptr));
+    return PD_OK;
 }
 
 int pd_dispatch_host(int family, const void* params, size_t params_bytes, int math_mode, const int64_t grid[3],

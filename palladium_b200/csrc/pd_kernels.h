@@ -50,6 +50,14 @@ struct PdGsArgs {
     int row_lo, row_hi;  // rows updated by this launch: [row_lo, row_hi)
     int periodic_rows;
     float du, dv, f, fk, dt;
+    // Row slabs on several GPUs: when `push` is set, output rows [top_lo, top_hi)
+    // are also stored to the upper neighbour's fields at row + up_shift, and rows
+    // [bot_lo, bot_hi) to the lower neighbour's at row + dn_shift (its ghost rows;
+    // peer device memory, plain stores over NVLink).
+    int push;
+    int top_lo, top_hi, up_shift;
+    int bot_lo, bot_hi, dn_shift;
+    float *up_u, *up_v, *dn_u, *dn_v;
 };
 
 struct PdDfLvArgs {

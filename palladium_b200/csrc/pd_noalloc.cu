@@ -121,7 +121,7 @@ extern "C" int pd_gray_scott_static(const pd_gray_scott_params* p, int math_mode
         return PD_OK;
     }
 
-    PdGsArgs a;
+    PdGsArgs a = {};
     a.rows_alloc = (int)rows_alloc;
     a.cols = (int)p->cols;
     a.periodic_rows = p->halo == 0 ? 1 : 0;

@@ -199,13 +199,25 @@ class GrayScottSlab:
     overlap : run the exchange on a second stream behind the interior rows
         (`_advance_overlapped`).  Correct and tested, but it measured no gain at
         any halo depth (the exchange is latency, not bandwidth), so it is off.
+    push : the exchange from inside the compute kernel.  The slab's fields live in
+        memory the neighbours have mapped (CUDA IPC); the final launch of every
+        call stores the boundary rows to its own output and, from the same
+        registers, into the neighbours' ghost rows over NVLink, and the only
+        collective left is a one-element all-reduce that orders "everyone's call
+        has finished" before the next call (nothing waits inside a kernel).  Two
+        output sets alternate, so a neighbour never reads the set being written.
+        CUDA step function only; the first call still fills the ghost rows with
+        the point-to-point exchange.
     """
 
     def __init__(self, u, v, rows_total: int, *, halo: int = 4, constants: dict | None = None, math_mode="fast",
-                 group=None, step_fn: Callable | None = None, overlap: bool = False):
+                 group=None, step_fn: Callable | None = None, overlap: bool = False, push: bool = False):
         import torch
 
         self.overlap = overlap
+        self.push = bool(push)
+        if self.push and step_fn is not None:
+            raise ValueError("push=True needs the CUDA step function (it stores into the neighbours' device memory)")
         self._comm = None
         self._out = None
 
@@ -233,6 +245,124 @@ class GrayScottSlab:
         self.up = (self.rank - 1) % self.world    # owns the rows above ours
         self.down = (self.rank + 1) % self.world  # owns the rows below ours
         self.exchanges = 0
+        self.pushes = 0
+        if self.push:
+            self._setup_push()
+
+    # -- exchange from inside the kernel ---------------------------------------------
+    def _setup_push(self) -> None:
+        """Move the fields into IPC-exportable allocations (two sets), trade the
+        handles with the neighbours and map theirs."""
+        import torch
+
+        from . import _native
+
+        shape = (self.rows + 2 * self.halo, self.cols)
+        nbytes = shape[0] * shape[1] * 4
+        if self.u.dtype != torch.float32:
+            raise ValueError("push=True needs float32 fields")
+        device = self.u.device
+
+        class _Raw:   # a device allocation seen through the CUDA array interface
+            def __init__(self, ptr):
+                self.ptr = ptr
+                self.__cuda_array_interface__ = {"shape": shape, "typestr": "<f4", "data": (ptr, False), "version": 3,
+                                                 "strides": None}
+
+        self._raw, self._sets = [], []
+        with torch.cuda.device(device):
+            for _ in range(2):
+                fields = []
+                for _f in range(2):
+                    raw = _Raw(_native.peer_alloc(nbytes))
+                    self._raw.append(raw)
+                    fields.append(torch.as_tensor(raw, device=device))
+                self._sets.append(tuple(fields))
+        self._sets[0][0].copy_(self.u)
+        self._sets[0][1].copy_(self.v)
+        self._sets[1][0].zero_()
+        self._sets[1][1].zero_()
+        self.u, self.v = self._sets[0]
+        self._cur = 0
+        self._ghosts_valid = False
+        torch.cuda.synchronize(device)
+        mine = (self.rows, [_native.peer_export(raw.ptr) for raw in self._raw])   # order: set0 u, set0 v, set1 u, set1 v
+        if self.world == 1:
+            everyone = [mine]
+        else:
+            dist = _dist()
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, mine, group=self.group)
+        self._opened: dict = {}
+
+        def pointers(rank):
+            if rank == self.rank:
+                return [raw.ptr for raw in self._raw]
+            if rank not in self._opened:
+                with torch.cuda.device(device):
+                    self._opened[rank] = [_native.peer_open(h) for h in everyone[rank][1]]
+            return self._opened[rank]
+
+        up_ptrs, down_ptrs = pointers(self.up), pointers(self.down)
+        self._neighbours = [
+            _native.GsNeighbours(up_ptrs[2 * k], up_ptrs[2 * k + 1], everyone[self.up][0],
+                                 down_ptrs[2 * k], down_ptrs[2 * k + 1], everyone[self.down][0])
+            for k in range(2)
+        ]
+        self._flag = torch.zeros(1, dtype=torch.float32, device=device)
+        if self.world > 1:
+            _dist().barrier(group=self.group)   # every rank has mapped its neighbours before anyone pushes
+
+    def _advance_push(self, k: int) -> None:
+        import torch
+
+        from . import _native
+        from .math_mode import math_mode_ordinal
+
+        if not self._ghosts_valid:
+            self.exchange()                      # the first call: ghost rows from the initial state
+        c = self.constants
+        defaults = dict(du=0.16, dv=0.08, f=0.035, k=0.065, dt=1.0)
+        defaults.update(c)
+        params = _native.GrayScottParams(defaults["du"], defaults["dv"], defaults["f"], defaults["k"], defaults["dt"],
+                                         k, self.rows, self.cols, self.halo)
+        out = 1 - self._cur
+        (u, v), (uo, vo) = self._sets[self._cur], self._sets[out]
+        with torch.cuda.device(u.device):
+            _native.gray_scott_slab_push(params, math_mode_ordinal(self.math_mode), u.data_ptr(), v.data_ptr(),
+                                         uo.data_ptr(), vo.data_ptr(), self._neighbours[out],
+                                         torch.cuda.current_stream().cuda_stream)
+        if self.world > 1:
+            # orders "every rank's call (and its stores into our ghost rows) has finished"
+            # before anyone's next call reads them
+            _dist().all_reduce(self._flag, group=self.group)
+        self._cur = out
+        self.u, self.v = self._sets[out]
+        self._ghosts_valid = True
+        self.pushes += 1
+
+    def close(self) -> None:
+        """Unmap the neighbours' memory and free this slab's exportable allocations
+        (push mode; call on every rank, after a barrier, when the slab is done)."""
+        if not self.push or not getattr(self, "_raw", None):
+            return
+        import torch
+
+        from . import _native
+
+        torch.cuda.synchronize(self.u.device)
+        self.u, self.v = self.u.clone(), self.v.clone()
+        with torch.cuda.device(self.u.device):
+            for ptrs in self._opened.values():
+                for ptr in ptrs:
+                    _native.peer_close(ptr)
+            self._opened = {}
+            if self.world > 1:
+                _dist().barrier(group=self.group)    # nobody still maps our memory
+            for raw in self._raw:
+                _native.peer_free(raw.ptr)
+        self._raw, self._sets = [], []
+        self.push = False
 
     # -- communication ----------------------------------------------------------------
     def exchange(self) -> None:
@@ -297,7 +427,9 @@ class GrayScottSlab:
                    and self.rows >= 2 * self.halo + 1)
         while done < steps:
             k = min(self.halo, steps - done)
-            if overlap:
+            if self.push:
+                self._advance_push(k)
+            elif overlap:
                 self._advance_overlapped(k)
             else:
                 self.exchange()
