@@ -53,6 +53,10 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="rk4_lv")
     ap.add_argument("--n", type=int, default=0, help="units per GPU (0 = workload default)")
+    ap.add_argument("--push", type=int, default=1,
+                    help="gray_scott on several GPUs: 1 = halo rows stored into the neighbours' memory by the "
+                         "compute kernel, 0 = point-to-point exchange between calls")
+    ap.add_argument("--halo", type=int, default=16, help="gray_scott on several GPUs: ghost rows per side")
     ap.add_argument("--math-mode", default="fast", choices=["safe", "relaxed", "fast"])
     ap.add_argument("--no-families", action="store_true", help="skip the short per-family measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")

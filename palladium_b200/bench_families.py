@@ -338,12 +338,13 @@ def run(args, rank: int, local_rank: int, world: int, barrier, max_over_ranks) -
     elif name == "gray_scott":
         size = args.n or 8192
         rows_total = size * world if world > 1 else size
-        halo = 16
+        halo = int(getattr(args, "halo", 16))
+        push = bool(getattr(args, "push", 1)) and world > 1
         lo, hi = sharded.partition(rows_total, world, rank)
         u = torch.rand((hi - lo, size), device="cuda") * 0.5 + 0.5
         v = torch.rand((hi - lo, size), device="cuda") * 0.25
         cfg = {k: v_ for k, v_ in W.GRAY_SCOTT_CONFIG.items() if k not in ("steps", "size", "seed")}
-        slab = sharded.GrayScottSlab(u, v, rows_total, halo=halo, constants=cfg, math_mode=args.math_mode)
+        slab = sharded.GrayScottSlab(u, v, rows_total, halo=halo, constants=cfg, math_mode=args.math_mode, push=push)
         per_step = 64
         for _ in range(warmup):
             slab.advance(per_step)
@@ -363,7 +364,9 @@ def run(args, rank: int, local_rank: int, world: int, barrier, max_over_ranks) -
                      "scaling": "weak", "gpu_launches": steps * per_step,
                      "config": {"workload": "gray_scott_periodic", "rows": rows_total, "cols": size,
                                 "stencil_steps_per_bench_step": per_step, "halo": halo, "math_mode": args.math_mode,
-                                "parallelism": f"row slabs x{world}, halo exchange every {halo} steps",
+                                "parallelism": f"row slabs x{world}, halo exchange every {halo} steps"
+                                               + (" from inside the compute kernel (peer stores over NVLink)" if push
+                                                  else " (point-to-point sends)" if world > 1 else ""),
                                 "l2": "fields are 268 MB each at 8192^2, larger than the 126 MB L2"},
                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
                                   "traffic": None, "peak_source": note}})

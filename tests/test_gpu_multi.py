@@ -51,6 +51,14 @@ def _worker(rank, world, port, out_dir):
             slab.advance(steps)
             results.append(slab.owned())
         assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+        # the exchange from inside the kernel: boundary rows stored into the neighbours' memory
+        pushed = sharded.GrayScottSlab(torch.from_numpy(u0[lo:hi]).cuda(), torch.from_numpy(v0[lo:hi]).cuda(), rows,
+                                       halo=halo, constants=dict(oracle.GS_DEFAULTS), math_mode="safe", push=True)
+        pushed.advance(steps)
+        pu, pv = (t.clone() for t in pushed.owned())
+        assert pushed.exchanges == 1 and pushed.pushes == -(-steps // halo)
+        pushed.close()
+        assert torch.equal(pu, results[0][0]) and torch.equal(pv, results[0][1])
         u, v = results[0]
         cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=64)
         res = sharded.gbm_monte_carlo(W.gbm_key(0), 100_003, cfg, math_mode="safe")
