@@ -265,6 +265,14 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
             plan->kernel_name = pd_rtc_kernel_name(p);
             plan->block[0] = b;
             plan->grid[0] = (n + b - 1) / b;
+            if (p->method == PD_ODE_BS32) {
+                // persistent warps, about 1024 threads per SM (as for the Van der Pol kernel)
+                int per_sm = 1024 / b > 0 ? 1024 / b : 1;
+                int64_t g = (int64_t)dev.sms * per_sm;
+                if (g > plan->grid[0]) g = plan->grid[0];
+                plan->grid[0] = g > 0 ? g : 1;
+                plan->scratch_bytes = 256;
+            }
             if (dev.present) {
                 // compiled on the first use of this source text, cached afterwards
                 rc = pd_rtc_get(p, math_mode, dev.device, b, &plan->rtc, err, err_cap);
@@ -747,6 +755,10 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             if (p->method == PD_ODE_BS32) {
                 a.coeff1 = (float)((p->icoeff + p->pcoeff) / (double)p->error_order);
                 a.coeff2 = (float)(-p->pcoeff / (double)p->error_order);
+                a.cursor = (unsigned long long*)scratch;
+                a.refill_every = (int)knob("vdp_refill_every");
+                if (a.refill_every < 1) a.refill_every = 1;
+                PD_CUDA_TRY(cudaMemsetAsync(scratch, 0, 256, st));
             }
             rc = pd_rtc_launch(plan.rtc, plan.grid[0], b, a, (void*)st, err, err_cap);
             if (rc) return rc;

@@ -22,8 +22,10 @@ struct PdOdeArgs {
     const float* in[16];   // dim state arrays, then nparam parameter arrays, each (n) f32
     float* out[16];        // RK4: dim arrays.  BS3(2): t, dim arrays, steps, rejected, real
     long long n;
+    unsigned long long* cursor;   // BS3(2): the next unclaimed system (zeroed before the launch)
     int steps;             // RK4 step count
     int max_steps;         // BS3(2) attempt limit
+    int refill_every;      // BS3(2): attempts between refill checks
     float h_half, h_full, h_sixth;
     float t1, rtol, atol, dt0, safety, factor_min, factor_max, coeff1, coeff2;
 };

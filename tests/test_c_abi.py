@@ -105,3 +105,35 @@ def test_missing_library_is_an_emit_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_native, "_lib", None)
     with pytest.raises(EmitError, match="isn't built"):
         _native.library()
+
+
+def test_pointer_carrying_structs_match_the_compilers_layout(tmp_path):
+    """The parameter blocks with pointers in them are checked against the C
+    compiler itself: size and the offset of every field."""
+    import subprocess
+
+    structs = {
+        "pd_custom_ode_params": _native.CustomOdeParams,
+        "pd_source_kernel_params": _native.SourceKernelParams,
+        "pd_gs_neighbours": _native.GsNeighbours,
+    }
+    lines = ['#include <stddef.h>', '#include <stdio.h>', f'#include "{ROOT / "include" / "palladium_cuda.h"}"',
+             "int main(void) {"]
+    for cname, cls in structs.items():
+        lines.append(f'  printf("{cname} size %zu\\n", sizeof({cname}));')
+        for field, _ in cls._fields_:
+            lines.append(f'  printf("{cname} {field} %zu\\n", offsetof({cname}, {field}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c11", str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    seen = {}
+    for line in out.splitlines():
+        cname, field, value = line.split()
+        seen[(cname, field)] = int(value)
+    for cname, cls in structs.items():
+        assert seen[(cname, "size")] == ctypes.sizeof(cls), cname
+        for field, _ in cls._fields_:
+            assert seen[(cname, field)] == getattr(cls, field).offset, (cname, field)

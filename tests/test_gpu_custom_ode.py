@@ -136,3 +136,34 @@ def test_explain_reports_the_compiled_kernel():
     text = str(info)
     assert "pd_ode_rk4" in text
     assert info.regs > 0 and info.blocks_per_sm > 0 and info.msl_lines == 3
+
+
+def test_concurrent_first_calls_compile_once_and_agree():
+    """Sixteen threads hit a source text nobody has compiled yet (the reference's
+    robustness test does the same with a fresh kernel, tests/test_17_robustness.py:22-78):
+    the native cache is mutex-guarded, every thread gets the same results."""
+    import threading
+
+    n = 2048
+    ins = lorenz_ensemble(n, seed=77)
+    rhs = LORENZ + "\n// concurrent-first-call variant"       # a text no other test has compiled
+    call = H.custom_solver(n, rhs, 3, 3, dt=0.004, steps=64)
+    want = oracle_custom.rk4(LORENZ, 3, 3, ins, dt=0.004, steps=64)
+    results, errors = [None] * 16, []
+
+    def work(i):
+        try:
+            results[i] = call(*ins)
+        except Exception as exc:  # noqa: BLE001
+            errors.append(exc)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(16)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors
+    assert len(call.cache) == 1
+    for got in results:
+        for g, w in zip(got, want):
+            np.testing.assert_array_equal(g, w)
