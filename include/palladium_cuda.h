@@ -39,7 +39,7 @@ typedef enum pd_status {
     PD_ERR_INVALID_ARGUMENT = 1, /* maps to xla::ffi::Error::InvalidArgument (palladium_ffi.cpp:118-121) */
     PD_ERR_INTERNAL = 2,         /* maps to xla::ffi::Error::Internal (palladium_ffi.cpp:126,139,147,167) */
     PD_ERR_CUDA = 3,             /* a CUDA runtime call failed; message carries cudaGetErrorString */
-    PD_ERR_DEVICE_STATUS = 4     /* a kernel reported a non-zero device status word */
+    PD_ERR_DEVICE_STATUS = 4     /* reserved for a kernel-reported status word; no kernel of this library waits on another, so none reports one */
 } pd_status;
 
 /* MRMathMode ordinals as the reference passes them (src/palladium/ffi.py:38;
