@@ -39,7 +39,7 @@ def _worker(rank, world, port, out_dir):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        rows, cols, steps, halo = 256, 512, 18, 4
+        rows, cols, steps, halo = 250, 512, 18, 4   # 250 rows: unequal slabs on 4 ranks (63, 63, 62, 62)
         u0, v0 = W.gray_scott_initial_state(512, seed=11, patches=16, patch=32)
         u0, v0 = u0[:rows].copy(), v0[:rows].copy()
         lo, hi = sharded.partition(rows, world, rank)
@@ -95,7 +95,7 @@ def test_two_gpus_halo_exchange_and_all_reduce(tmp_path):
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    rows, steps = 256, 18
+    rows, steps = 250, 18
     u0, v0 = W.gray_scott_initial_state(512, seed=11, patches=16, patch=32)
     want_u, want_v = oracle.gray_scott(u0[:rows].copy(), v0[:rows].copy(), steps=steps)
     cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=64)
