@@ -287,7 +287,8 @@ def test_stepper_rejects_mismatched_feedback():
 
 # ------------------------------------------------------------------ the example scripts run
 @pytest.mark.parametrize("script", ["01_ode_ensembles", "02_adaptive_lockstep", "03_sde_montecarlo",
-                                    "04_reaction_diffusion", "05_df32_precision", "06_custom_rhs"])
+                                    "04_reaction_diffusion", "05_df32_precision", "06_custom_rhs",
+                                    "07_multi_gpu_stencil"])
 def test_example_scripts_run(script):
     import runpy
     from pathlib import Path

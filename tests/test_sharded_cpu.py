@@ -138,6 +138,8 @@ def test_gray_scott_single_rank_wraps_its_own_halo():
 
 def test_slab_argument_checks():
     u = torch.zeros(8, 4)
+    with pytest.raises(ValueError, match="push=True needs the CUDA step function"):
+        sharded.GrayScottSlab(u, u, 8, halo=2, step_fn=_np_slab_step, push=True)
     with pytest.raises(ValueError, match="expected fields of shape"):
         sharded.GrayScottSlab(u, u, 16, halo=2, step_fn=_np_slab_step)
     with pytest.raises(ValueError, match="cannot serve"):
