@@ -215,7 +215,7 @@ def test_cache_is_per_shape_signature():
 
 def test_concurrent_first_calls_bind_once(monkeypatch):
     # tests/test_17_robustness.py:22-50: 16 threads, exactly one compile per shape
-    import palladium_b200 as package
+    from palladium_b200 import call as package
 
     binds = []
     real_bind = package.bind
