@@ -368,6 +368,8 @@ def main():
         if not args.no_cpu:
             rate, kind, cores, sample = cpu_rk4(1 << 20)
             cpu_baseline = {"value": rate, "unit": "trajectory-steps/s", "cores": cores, "kind": kind, "sample": sample}
+            one, _, _, one_sample = cpu_rk4(1 << 16, threads=1)   # the same code on a single host thread
+            cpu_baseline["single_thread"] = {"value": one, "cores": 1, "sample": one_sample}
         if world == 1 and not args.no_families:
             try:
                 from palladium_b200 import bench_families
