@@ -193,6 +193,27 @@ def reference_kernel_fixture():
         kernel(PN.Ref(u), PN.Ref(v), PN.Ref(uo), PN.Ref(vo))
         u, v = uo, vo
     out.update(gs_u0=u0, gs_v0=v0g, gs_u=np.asarray(u), gs_v=np.asarray(v))
+    # the five-output adaptive kernel of the reference's own test, on that test's own inputs:
+    # tests/test_08_adaptive.py:33-142 (kernel), :157-171 (`_inputs`), the rng fixture of
+    # tests/conftest.py:21-23 (seed 17); case (a) mild ensemble, case (b) 2 % stiff members
+    test08 = REFERENCE_ROOT / "tests" / "test_08_adaptive.py"
+    consts = dict(X0=2.0, V0=0.0, DT0=0.01, T1=10.0, MAX_STEPS=6000, RTOL=1e-5, ATOL=1e-7, pcoeff=0.4, icoeff=0.3,
+                  error_order=3)
+    n = 256
+    kernel = PN.load_kernel(test08, "vdp_adaptive_kernel", (n,), consts)
+    helpers = {"np": np, **consts}
+    for name in ("_mu_ensemble", "_inputs"):
+        node = PN.extract_function(test08, name)
+        import ast
+
+        exec(compile(ast.Module(body=[node], type_ignores=[]), str(test08), "exec"), helpers)
+    rng = np.random.default_rng(seed=17)
+    for tag, stiff in (("mild", 0.0), ("stiff", 0.02)):
+        x0, v0, mu = helpers["_inputs"](rng, n, stiff_fraction=stiff)
+        outs = [PN.Ref(PN.f32(np.zeros(n))) for _ in range(5)]
+        kernel(PN.Ref(PN.f32(x0)), PN.Ref(PN.f32(v0)), PN.Ref(PN.f32(mu)), *outs)
+        out[f"test08_{tag}_in"] = np.stack([x0, v0, mu])
+        out[f"test08_{tag}_out"] = np.stack([np.asarray(o.array) for o in outs])
     np.savez_compressed(HERE / "reference_kernels.npz", **out)
 
 

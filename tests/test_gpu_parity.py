@@ -268,6 +268,28 @@ def test_kernels_against_the_references_own_kernel_functions():
     np.testing.assert_allclose(payoff, g["gbm_payoff"], rtol=1e-5, atol=2e-3)
 
 
+@pytest.mark.parametrize("mode", [RELAXED, SAFE, FAST])
+def test_adaptive_kernel_passes_the_references_own_test(mode):
+    """tests/test_08_adaptive.py:174-199 in the reference, cases (a) and (b), with
+    its kernel's outputs (run on NumPy stand-ins, tests/golden/make_golden.py) in
+    the place of `f.interpret`: same inputs, same tolerances."""
+    from pathlib import Path
+
+    g = np.load(Path(__file__).resolve().parent / "golden" / "reference_kernels.npz")
+    cfg = dict(t1=10.0, rtol=1e-5, atol=1e-7, dt0=0.01, max_steps=6000)
+    n = g["test08_mild_in"].shape[1]
+    solve = H.vdp_solver(n, outputs=5, math_mode=mode, **cfg)
+    got_t, got_x, got_v, got_steps, got_rejected = solve(*g["test08_mild_in"])
+    want_t, want_x, want_v, want_steps, want_rejected = g["test08_mild_out"]
+    np.testing.assert_allclose(got_t, want_t, rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(got_x, want_x, rtol=1e-3, atol=1e-4)
+    np.testing.assert_allclose(got_v, want_v, rtol=1e-3, atol=1e-4)
+    np.testing.assert_allclose(got_steps, want_steps, rtol=0, atol=20)
+    np.testing.assert_allclose(got_rejected, want_rejected, rtol=0, atol=20)
+    got_t, *_ = solve(*g["test08_stiff_in"])
+    np.testing.assert_allclose(got_t, 10.0, rtol=0, atol=1e-4)
+
+
 def test_df32_kernel_against_the_references_kernel_text():
     """The fixture: the reference's DF32_KERNEL text compiled for the CPU on the
     oracle's df32 prelude (tests/golden/make_golden.py)."""

@@ -416,3 +416,16 @@ def test_df32_kernel_structure_equals_the_references_kernel_text():
     x, y = oracle.lv_rk4_df32(*g["lv_inputs"], dt=0.01, steps=500)
     np.testing.assert_array_equal(x, g["x"])
     np.testing.assert_array_equal(y, g["y"])
+
+
+def test_oracle_equals_the_references_test_kernel_on_its_own_inputs():
+    """The five-output adaptive kernel of tests/test_08_adaptive.py:33-142 in the
+    reference, run on that test's own inputs (`_inputs`, rng seed 17): the mild
+    ensemble of its case (a) and the 2 % stiff ensemble of its case (b)."""
+    g = load("reference_kernels")
+    for tag in ("mild", "stiff"):
+        got = oracle.vdp_bs32(*g[f"test08_{tag}_in"], pow="libm", t1=10.0, rtol=1e-5, atol=1e-7, dt0=0.01,
+                              max_steps=6000)
+        for have, want, name in zip(got[:5], g[f"test08_{tag}_out"], ("t", "x", "v", "steps", "rejected")):
+            np.testing.assert_array_equal(have, want, err_msg=f"{tag} {name}")
+    assert np.all(g["test08_stiff_out"][0] == 10.0) and g["test08_stiff_in"][2].max() > 300.0
