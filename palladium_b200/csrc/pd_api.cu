@@ -57,7 +57,7 @@ std::map<std::string, int64_t>& tuning() {
         {"gs_fuse", 4},              // steps fused per launch by variant 2 (2..4)
         {"gs_persistent", 0},        // variant 2: one tile per block (0, faster at K = 4) or persistent blocks with cp.async prefetch (1)
         {"df32_block", 128},
-        {"host_chunks", 32},         // chunks a large host-buffer call is cut into
+        {"host_chunks", -1},         // chunks a large host-buffer call is cut into (-1 = by size, 0 = ramped sizes)
         {"time_kernels", 0},
     };
     return t;
@@ -949,10 +949,41 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
         }
     }
     if (chunked) {
-        int64_t want_chunks = knob("host_chunks");
-        if (want_chunks < 1) want_chunks = 1;
-        int64_t chunk = ((n + want_chunks - 1) / want_chunks + 4095) / 4096 * 4096;  // 16 KiB-aligned slices
-        if (chunk < ((int64_t)1 << 16)) chunk = (int64_t)1 << 16;
+        // Chunk boundaries.  host_chunks > 0: that many equal chunks.  host_chunks == 0:
+        // a ramp -- small chunks first and last, large ones between -- so that the
+        // upload of the first chunk and the download of the last one, which nothing
+        // can hide, are short, while most of the work runs in launches large enough
+        // for the kernels' best configuration.
+        std::vector<int64_t> bounds;   // chunk c covers [bounds[c], bounds[c + 1])
+        {
+            int64_t want_chunks = knob("host_chunks");
+            if (want_chunks < 0) {
+                // about 2^17 trajectories per chunk measured best from 2^20 to 2^22 (8 / 16 / 32
+                // chunks); beyond that more, larger chunks
+                want_chunks = n >> 17;
+                if (want_chunks < 8) want_chunks = 8;
+                if (want_chunks > 48) want_chunks = 48;
+            }
+            if (want_chunks > 0) {
+                int64_t chunk = ((n + want_chunks - 1) / want_chunks + 4095) / 4096 * 4096;  // 16 KiB-aligned slices
+                if (chunk < ((int64_t)1 << 16)) chunk = (int64_t)1 << 16;
+                for (int64_t lo = 0; lo < n; lo += chunk) bounds.push_back(lo);
+            } else {
+                static const int ramp64[] = {1, 1, 2, 4, 8, 8, 8, 8, 8, 8, 4, 2, 1, 1};
+                static const int ramp32[] = {1, 1, 2, 4, 8, 8, 4, 2, 1, 1};
+                static const int ramp16[] = {1, 1, 2, 4, 4, 2, 1, 1};
+                const int* ramp = ramp16; int parts = 8, units = 16;
+                if (n >= ((int64_t)1 << 22)) { ramp = ramp64; parts = 14; units = 64; }
+                else if (n >= ((int64_t)1 << 21)) { ramp = ramp32; parts = 10; units = 32; }
+                const int64_t unit = (n / units + 4095) / 4096 * 4096;
+                int64_t lo = 0;
+                for (int i = 0; i < parts && lo < n; ++i) {
+                    bounds.push_back(lo);
+                    lo += unit * ramp[i];
+                }
+            }
+            bounds.push_back(n);
+        }
         bool any_broadcast = false;
         for (int i = 0; i < n_in; ++i) {
             if (in_item[i] == 0 && in_bytes[i]) {
@@ -972,8 +1003,9 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
         std::vector<const void*> c_in(n_in);
         std::vector<void*> c_out(n_out);
         std::vector<size_t> c_in_bytes(n_in), c_out_bytes(n_out);
-        for (int64_t lo = 0; lo < n && rc == PD_OK; lo += chunk, ++c) {
-            const int64_t len = (n - lo < chunk) ? n - lo : chunk;
+        for (; c + 1 < (int)bounds.size() && rc == PD_OK; ++c) {
+            const int64_t lo = bounds[c];
+            const int64_t len = bounds[c + 1] - lo;
             cudaStream_t st = hs.streams[c % kHostStreams];
             for (int i = 0; i < n_in; ++i) {
                 if (in_item[i]) {
