@@ -57,6 +57,7 @@ std::map<std::string, int64_t>& tuning() {
         {"gs_fuse", 4},              // steps fused per launch by variant 2 (2..4)
         {"gs_persistent", 0},        // variant 2: one tile per block (0, faster at K = 4) or persistent blocks with cp.async prefetch (1)
         {"df32_block", 128},
+        {"host_streams", 3},         // streams the chunks of a host-buffer call rotate over (1..8)
         {"host_chunks", -1},         // chunks a large host-buffer call is cut into (-1 = by size, 0 = ramped sizes)
         {"time_kernels", 0},
     };
@@ -781,11 +782,11 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
 }
 
 // Per-thread staging state for pd_dispatch_host.
-const int kHostStreams = 3;
+const int kHostStreams = 8;   // streams created per staging thread; `host_streams` of them are used
 struct HostStaging {
     int device = -1;
     cudaStream_t stream = nullptr;                 // stream 0, also used for unchunked calls
-    cudaStream_t streams[kHostStreams] = {nullptr, nullptr, nullptr};
+    cudaStream_t streams[kHostStreams] = {};
     cudaEvent_t broadcast_done = nullptr;
     std::vector<ScratchSlot> slots;
     ~HostStaging() {
@@ -984,6 +985,8 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
             }
             bounds.push_back(n);
         }
+        int n_streams = (int)knob("host_streams");
+        n_streams = n_streams < 1 ? 1 : (n_streams > kHostStreams ? kHostStreams : n_streams);
         bool any_broadcast = false;
         for (int i = 0; i < n_in; ++i) {
             if (in_item[i] == 0 && in_bytes[i]) {
@@ -993,7 +996,7 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
         }
         if (any_broadcast) {
             PD_CUDA_TRY(cudaEventRecord(hs.broadcast_done, hs.streams[0]));
-            for (int sidx = 1; sidx < kHostStreams; ++sidx)
+            for (int sidx = 1; sidx < n_streams; ++sidx)
                 PD_CUDA_TRY(cudaStreamWaitEvent(hs.streams[sidx], hs.broadcast_done, 0));
         }
         unsigned char local_params[256];
@@ -1006,7 +1009,7 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
         for (; c + 1 < (int)bounds.size() && rc == PD_OK; ++c) {
             const int64_t lo = bounds[c];
             const int64_t len = bounds[c + 1] - lo;
-            cudaStream_t st = hs.streams[c % kHostStreams];
+            cudaStream_t st = hs.streams[c % n_streams];
             for (int i = 0; i < n_in; ++i) {
                 if (in_item[i]) {
                     const size_t off = (size_t)lo * in_item[i];
