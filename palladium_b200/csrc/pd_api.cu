@@ -47,9 +47,10 @@ std::map<std::string, int64_t>& tuning() {
     static std::map<std::string, int64_t> t = {
         {"lv_items_per_thread", 0},  // 0 = choose from N and alignment
         {"lv_block", 0},             // 0 = choose from N
-        {"vdp_variant", 1},          // 0 direct, 1 persistent warps with lane refill
+        {"vdp_variant", 2},          // 0 direct, 1 persistent warps with lane refill, 2 refill + tail compaction
         {"vdp_block", 128},
         {"vdp_refill_every", 8},     // attempts between refill checks
+        {"vdp_compact_every", 16},   // variant 2: refill rounds between block-level compactions
         {"vdp_blocks_per_sm", 0},    // 0 = about 1024 resident threads per SM
         {"gbm_block", 256},
         {"gbm_blocks_per_sm", 0},
@@ -231,6 +232,7 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "vdp_bs32: error_order must be positive");
             const int variant = (int)knob("vdp_variant");
             int b = req_block ? req_block : (int)knob("vdp_block");
+            if (variant == 2) b = 256;   // the compaction kernel's shared arrays are sized for 256 threads
             plan->variant = variant;
             plan->kernel = mt->kernel_ptr(family, variant);
             plan->block[0] = b;
@@ -238,7 +240,7 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 plan->kernel_name = "pd_vdp_direct_kernel";
                 plan->grid[0] = (n + b - 1) / b;
             } else {
-                plan->kernel_name = "pd_vdp_refill_kernel";
+                plan->kernel_name = variant == 2 ? "pd_vdp_compact_kernel" : "pd_vdp_refill_kernel";
                 // About 1024 resident threads per SM measured best: enough warps to
                 // hide the divide / pow latencies, and few enough threads that each one
                 // integrates many trajectories, which evens out the heavy-tailed work.
@@ -618,9 +620,17 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             a.safety = (float)p->safety; a.factor_min = (float)p->factor_min; a.factor_max = (float)p->factor_max;
             a.coeff1 = (float)((p->icoeff + p->pcoeff) / (double)p->error_order);
             a.coeff2 = (float)(-p->pcoeff / (double)p->error_order);
-            if (plan.variant == 1) {
+            if (plan.variant >= 1) {
                 a.cursor = (unsigned long long*)scratch;
                 PD_CUDA_TRY(cudaMemsetAsync(scratch, 0, 256, st));
+            }
+            if (plan.variant == 2) {
+                a.compact_every = (int)knob("vdp_compact_every");
+                if (a.compact_every < 1) a.compact_every = 1;
+                // list scheduling: the last lane finishes within (average load + longest job) rounds
+                const long long lanes = (long long)plan.grid[0] * b;
+                const long long per_job = a.max_steps / a.refill_every + 2;
+                a.round_limit = ((n + lanes - 1) / lanes + 2) * per_job + 2LL * a.compact_every;
             }
             PD_CUDA_TRY(mt->vdp_bs32(a, plan.variant, (int)plan.grid[0], b, st));
             break;

@@ -28,6 +28,8 @@ struct PdVdpArgs {
     int64_t n;
     int max_steps;
     int refill_every;  // attempts between two refill checks of a warp
+    int compact_every; // variant 2: refill rounds between two block-level compactions
+    long long round_limit;  // variant 2: upper bound on rounds (list-scheduling bound), a guard against endless loops
     float t1, rtol, atol, dt0, safety, factor_min, factor_max, coeff1, coeff2;
 };
 

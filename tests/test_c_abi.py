@@ -79,12 +79,12 @@ def test_params_size_is_checked():
 
 
 def test_tuning_knobs_round_trip():
-    assert _native.get_tuning("vdp_variant") == 1
+    assert _native.get_tuning("vdp_variant") == 2
     _native.set_tuning("vdp_variant", 0)
     try:
         assert _native.get_tuning("vdp_variant") == 0
     finally:
-        _native.set_tuning("vdp_variant", 1)
+        _native.set_tuning("vdp_variant", 2)
     with pytest.raises(KeyError):
         _native.set_tuning("no_such_knob", 1)
 

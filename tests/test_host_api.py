@@ -68,7 +68,7 @@ def test_explain_large_ensemble_uses_vector_items():
 
 def test_explain_other_families():
     d = H.vdp_solver(5000, outputs=6).explain(*[H.shaped(5000)] * 3)
-    assert d.cuda_kernel == "pd_vdp_refill_kernel" and d.scratch_bytes > 0
+    assert d.cuda_kernel == "pd_vdp_compact_kernel" and d.scratch_bytes > 0
     d = H.gs_solver(256, 256, steps=10).explain(H.shaped(256, 256), H.shaped(256, 256))
     assert d.cuda_kernel == "pd_gs_tb_kernel<4>" and d.launches == 3 and d.scratch_bytes == 2 * 256 * 256 * 4
     d = H.gs_solver(256, 256, steps=1).explain(H.shaped(256, 256), H.shaped(256, 256))
