@@ -77,7 +77,10 @@ typedef struct pd_lv_rk4_params {
     int64_t steps;
 } pd_lv_rk4_params;
 
-/* in:  x0,v0,mu (N) f32.
+/* in:  x0,v0,mu (N) f32 [, order (N) i32: the sequence in which the kernel's work
+ *      queue hands out the trajectories, a permutation of 0..N-1; results do not
+ *      depend on it, run time does (longest first is best); entries outside
+ *      [0, N) are skipped].
  * out_layout 0: t,x,v,steps,rejected,real  (6 x (N) f32)   examples/02:173-181
  * out_layout 1: t,x,v,steps,rejected       (5 x (N) f32)   tests/test_08_adaptive.py:33-142
  * out_layout 2: state (N,2) f32, accepted (N) i32, rejected (N) i32

@@ -475,7 +475,7 @@ bool all_aligned16(int n_in, const void* const* in, int n_out, void* const* out)
 
 // Expected buffer sizes for a family call.
 int expected_sizes(int family, const void* params, const int64_t grid[3], std::vector<size_t>* in,
-                   std::vector<size_t>* out, int n_out_given, char* err, size_t err_cap) {
+                   std::vector<size_t>* out, int n_in_given, int n_out_given, char* err, size_t err_cap) {
     const size_t n = (size_t)grid[0];
     switch (family) {
         case PD_FAMILY_LV_RK4:
@@ -483,7 +483,7 @@ int expected_sizes(int family, const void* params, const int64_t grid[3], std::v
             in->assign(6, 4 * n); out->assign(2, 4 * n); return PD_OK;
         case PD_FAMILY_VDP_BS32: {
             const pd_vdp_bs32_params* p = static_cast<const pd_vdp_bs32_params*>(params);
-            in->assign(3, 4 * n);
+            in->assign(n_in_given == 4 ? 4 : 3, 4 * n);   // optional 4th input: the hand-out order, (N) int32
             if (p->out_layout == 0) out->assign(6, 4 * n);
             else if (p->out_layout == 1) out->assign(5, 4 * n);
             else { out->assign(3, 4 * n); (*out)[0] = 8 * n; }
@@ -542,7 +542,7 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
     if (rc) return rc;
     if (family != PD_FAMILY_SOURCE) {   // a caller-written kernel defines its own buffer sizes
         std::vector<size_t> want_in, want_out;
-        rc = expected_sizes(family, params, grid, &want_in, &want_out, n_out, err, err_cap);
+        rc = expected_sizes(family, params, grid, &want_in, &want_out, n_in, n_out, err, err_cap);
         if (rc) return rc;
         rc = check_buffers("input", n_in, (int)want_in.size(), in_bytes, want_in.data(), in, err, err_cap);
         if (rc) return rc;
@@ -602,6 +602,7 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             PdVdpArgs a;
             memset(&a, 0, sizeof(a));
             a.x0 = (const float*)in[0]; a.v0 = (const float*)in[1]; a.mu = (const float*)in[2];
+            a.order = (n_in == 4 && plan.variant >= 1) ? (const int32_t*)in[3] : nullptr;
             if (p->out_layout == 2) {
                 if (!aligned(out[0], 8))
                     return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output 0: (N,2) state must be 8-byte aligned");
@@ -943,7 +944,7 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
     // inputs of chunk c+1 are uploading and the results of chunk c-1 are
     // downloading.  A buffer whose size is not proportional to the trajectory
     // count (the RNG key) is uploaded once and the chunk streams wait for it.
-    const bool per_item_family = family == PD_FAMILY_LV_RK4 || family == PD_FAMILY_VDP_BS32 ||
+    const bool per_item_family = family == PD_FAMILY_LV_RK4 || (family == PD_FAMILY_VDP_BS32 && n_in == 3) ||
                                  family == PD_FAMILY_LV_RK4_DF32 || family == PD_FAMILY_KEPLER_RK4_DF32 ||
                                  family == PD_FAMILY_CUSTOM_ODE ||
                                  ((family == PD_FAMILY_GBM_THREEFRY || family == PD_FAMILY_GBM_PCG) && n_out == 1);

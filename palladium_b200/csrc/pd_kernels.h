@@ -20,6 +20,7 @@ struct PdLvArgs {
 
 struct PdVdpArgs {
     const float *x0, *v0, *mu;
+    const int32_t* order;  // optional: the sequence in which the queue hands out trajectories (a permutation of 0..n-1)
     // any output pointer may be null
     float *t_out, *x_out, *v_out, *steps_out, *rejected_out, *real_out;
     float *state2_out;

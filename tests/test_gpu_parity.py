@@ -152,6 +152,36 @@ def test_vdp_safe_counts_bit_exact(n, variant):
         assert np.std(got[5]) > 0  # adaptivity is per trajectory (tests/test_08_adaptive.py:237-245)
 
 
+def test_vdp_hand_out_order_changes_scheduling_not_results():
+    import torch
+
+    from palladium_b200 import families, pl
+
+    n = 5000
+    cfg = dict(t1=5.0, rtol=1e-5, atol=1e-7, dt0=0.01, max_steps=6000)
+    ins = [torch.from_numpy(a).cuda() for a in W.van_der_pol_ensemble(n)]
+    sh = pl.ShapeDtypeStruct((n,), np.float32)
+    call = pd.cuda_call_jit(families.vdp_bs32(**cfg), grid=(n,), out_shape=(sh,) * 6, math_mode=SAFE)
+    plain = call(*ins)
+    rng = np.random.default_rng(0)
+    order = torch.from_numpy(rng.permutation(n).astype(np.int32)).cuda()
+    for got, want in zip(call(*ins, order), plain):
+        assert torch.equal(got, want)
+    by_cost = families.vdp_cost_order(*ins, **cfg)
+    assert sorted(by_cost.cpu().tolist()) == list(range(n))
+    for got, want in zip(call(*ins, by_cost), plain):
+        assert torch.equal(got, want)
+    # entries that are not trajectory indices are skipped, not dereferenced: the others still run
+    bad = order.clone()
+    bad[:10] = torch.tensor([-1, n, n + 5, 2 ** 30, -7, n, n, -1, -1, n], dtype=torch.int32)
+    skipped = order[:10].long()
+    out = call(*ins, bad)
+    keep = torch.ones(n, dtype=torch.bool, device="cuda")
+    keep[skipped] = False
+    for got, want in zip(out, plain):
+        assert torch.equal(got[keep], want[keep])
+
+
 def test_vdp_config_layout_int_counts():
     n = 777
     x0, v0, mu = W.van_der_pol_ensemble(n)
