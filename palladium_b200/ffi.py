@@ -129,6 +129,39 @@ class FfiCallable:
             return self._call_jax(args)
         return self._call_host(args)
 
+    def vmap(self, *args, in_axes=0):
+        """The call mapped over a leading batch axis, one dispatch per batch
+        element: what `jax.vmap` does to the reference's FFI call under
+        `vmap_method="sequential"` (src/palladium/ffi.py:118-125, 190-221).  As
+        there, a call built without a `vmap_method` refuses to be batched.
+        `in_axes`: 0 (every operand carries the batch axis first) or a sequence
+        with 0 / None per operand (None: the operand is shared by all elements).
+        Outputs are stacked along a new leading axis."""
+        if self._vmap_method is None:
+            raise NotImplementedError(
+                "this call was built without vmap_method: batching it needs "
+                "vmap_method='sequential' (or 'sequential_unrolled'), one dispatch per batch element")
+        axes = [in_axes] * len(args) if in_axes in (0, None) else list(in_axes)
+        if len(axes) != len(args) or any(a not in (0, None) for a in axes):
+            raise ValueError("in_axes must be 0, None, or one of them per operand")
+        sizes = {int(a.shape[0]) for a, ax in zip(args, axes) if ax == 0}
+        if len(sizes) != 1:
+            raise ValueError(f"mapped operands disagree on the batch size: {sorted(sizes)}")
+        batch = sizes.pop()
+        results = [self(*[a[i] if ax == 0 else a for a, ax in zip(args, axes)]) for i in range(batch)]
+        single = not isinstance(results[0], (tuple, list))
+        columns = [[r] for r in results] if single else [list(r) for r in results]
+        stacked = []
+        for k in range(len(columns[0])):
+            parts = [row[k] for row in columns]
+            if _is_torch_tensor(parts[0]):
+                import torch
+
+                stacked.append(torch.stack(parts))
+            else:
+                stacked.append(np.stack(parts))
+        return stacked[0] if single else tuple(stacked)
+
     # ---- torch CUDA tensors: stream-ordered, no synchronisation ----------------
     def _call_torch(self, args, out=None):
         import torch

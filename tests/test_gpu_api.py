@@ -285,6 +285,31 @@ def test_stepper_rejects_mismatched_feedback():
         pd.Stepper(H.gbm_solver(32, steps=4), key)
 
 
+def test_sequential_vmap_over_a_batch_axis():
+    """tests/test_11_ffi.py in the reference: vmap with 'sequential' dispatches once
+    per batch element; a call built without vmap_method refuses."""
+    import torch
+
+    n, batch = 257, 3
+    ins = W.lotka_volterra_ensemble(n * batch)
+    batched = [a.reshape(batch, n) for a in ins]
+    call = H.lv_solver(n, steps=40, call=pd.cuda_call_jit, vmap_method="sequential", math_mode=pd.MathMode.SAFE)
+    x, y = call.vmap(*batched)
+    wx, wy = oracle.lv_rk4(*ins, dt=0.01, steps=40)
+    np.testing.assert_array_equal(x.reshape(-1), wx)
+    np.testing.assert_array_equal(y.reshape(-1), wy)
+    # shared parameters, mapped initial states, device tensors
+    dev = [torch.from_numpy(a).cuda() for a in batched[:2]] + [torch.from_numpy(a[0].copy()).cuda() for a in batched[2:]]
+    x2, _ = call.vmap(*dev, in_axes=[0, 0, None, None, None, None])
+    assert x2.is_cuda and x2.shape == (batch, n)
+    np.testing.assert_array_equal(x2[0].cpu().numpy(), wx[:n])
+    plain = H.lv_solver(n, steps=40, call=pd.cuda_call_jit)
+    with pytest.raises(NotImplementedError, match="vmap_method"):
+        plain.vmap(*batched)
+    with pytest.raises(ValueError, match="batch size"):
+        call.vmap(batched[0], batched[1][:2], *batched[2:])
+
+
 # ------------------------------------------------------------------ the example scripts run
 @pytest.mark.parametrize("script", ["01_ode_ensembles", "02_adaptive_lockstep", "03_sde_montecarlo",
                                     "04_reaction_diffusion", "05_df32_precision", "06_custom_rhs",
