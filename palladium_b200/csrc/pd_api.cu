@@ -47,9 +47,10 @@ std::map<std::string, int64_t>& tuning() {
     static std::map<std::string, int64_t> t = {
         {"lv_items_per_thread", 0},  // 0 = choose from N and alignment
         {"lv_block", 0},             // 0 = choose from N
-        {"vdp_variant", 2},          // 0 direct, 1 persistent warps with lane refill, 2 refill + tail compaction
+        {"vdp_variant", 2},          // 0 direct, 1 lane refill, 2 refill + tail compaction, 3 two passes, longest predicted first
         {"vdp_block", 128},
         {"vdp_refill_every", 8},     // attempts between refill checks
+        {"vdp_pass_limit", 1000},    // variant 3: attempts after which pass one suspends a trajectory
         {"vdp_compact_every", 16},   // variant 2: refill rounds between block-level compactions
         {"vdp_blocks_per_sm", 0},    // 0 = about 1024 resident threads per SM
         {"gbm_block", 256},
@@ -232,15 +233,18 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "vdp_bs32: error_order must be positive");
             const int variant = (int)knob("vdp_variant");
             int b = req_block ? req_block : (int)knob("vdp_block");
-            if (variant == 2) b = 256;   // the compaction kernel's shared arrays are sized for 256 threads
-            plan->variant = variant;
+            int variant_used = variant;
+            // two passes make sense only when a trajectory can outlast the first one
+            if (variant == 3 && p->max_steps <= knob("vdp_pass_limit")) variant_used = 2;
+            if (variant_used >= 2) b = 256;   // the compaction kernel's shared arrays are sized for 256 threads
+            plan->variant = variant_used;
             plan->kernel = mt->kernel_ptr(family, variant);
             plan->block[0] = b;
             if (variant == 0) {
                 plan->kernel_name = "pd_vdp_direct_kernel";
                 plan->grid[0] = (n + b - 1) / b;
             } else {
-                plan->kernel_name = variant == 2 ? "pd_vdp_compact_kernel" : "pd_vdp_refill_kernel";
+                plan->kernel_name = plan->variant >= 2 ? "pd_vdp_compact_kernel" : "pd_vdp_refill_kernel";
                 // About 1024 resident threads per SM measured best: enough warps to
                 // hide the divide / pow latencies, and few enough threads that each one
                 // integrates many trajectories, which evens out the heavy-tailed work.
@@ -255,6 +259,13 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 if (g > needed) g = needed;
                 plan->grid[0] = g > 0 ? g : 1;
                 plan->scratch_bytes = 256;
+                if (plan->variant == 3) {
+                    // header (queue heads, count, bucket counters) + bucket and order per trajectory
+                    // + ten words of suspended state per trajectory
+                    const int64_t per = ((n + 63) / 64) * 64;
+                    plan->scratch_bytes = 1024 + 4 * per * 12;
+                    plan->launches = 4;
+                }
             }
             return PD_OK;
         }
@@ -625,7 +636,23 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
                 a.cursor = (unsigned long long*)scratch;
                 PD_CUDA_TRY(cudaMemsetAsync(scratch, 0, 256, st));
             }
-            if (plan.variant == 2) {
+            if (plan.variant == 3) {
+                // scratch: [0] queue head of pass one, [8] of pass two, [16] suspended count,
+                // [256] 64 bucket counters, [512] 64 write positions, [1024] per-trajectory arrays
+                char* base = (char*)scratch;
+                const int64_t per = ((n + 63) / 64) * 64;
+                a.cursor2 = (unsigned long long*)(base + 8);
+                a.n_susp = (unsigned long long*)(base + 16);
+                a.hist = (unsigned int*)(base + 256);
+                a.offsets = (unsigned int*)(base + 512);
+                a.bucket_of = (int32_t*)(base + 1024);
+                a.order2 = (int32_t*)(base + 1024 + 4 * per);
+                a.susp = (float*)(base + 1024 + 8 * per);
+                a.pass_limit = (int)knob("vdp_pass_limit");
+                PD_CUDA_TRY(cudaMemsetAsync(base, 0, 1024, st));
+                PD_CUDA_TRY(cudaMemsetAsync(a.bucket_of, 0xFF, 4 * (size_t)per, st));
+            }
+            if (plan.variant >= 2) {
                 a.compact_every = (int)knob("vdp_compact_every");
                 if (a.compact_every < 1) a.compact_every = 1;
                 // list scheduling: the last lane finishes within (average load + longest job) rounds

@@ -29,6 +29,19 @@ struct PdVdpArgs {
     int64_t n;
     int max_steps;
     int refill_every;  // attempts between two refill checks of a warp
+    // variant 3 (two passes): pass one suspends what is unfinished after `pass_limit`
+    // attempts and files it under a bucket of predicted remaining attempts; pass two
+    // resumes the suspended states, longest predicted first.
+    int pass_limit;                     // 0: never suspend
+    int resume;                         // lanes start from suspended states
+    const unsigned long long* n_dev;    // queue length in device memory (pass two), or null for n
+    unsigned long long* cursor2;        // pass two's queue head
+    unsigned long long* n_susp;         // number of suspended trajectories (written between the passes)
+    float* susp;                        // 10 arrays of n words: t, dt, x, v, k1x, k1v, prev_pow, rejected, real, iter
+    int32_t* bucket_of;                 // bucket of each suspended trajectory, -1 otherwise
+    unsigned int* hist;                 // 64 bucket counters
+    unsigned int* offsets;              // 64 write positions
+    int32_t* order2;                    // pass two's hand-out order
     int compact_every; // variant 2: refill rounds between two block-level compactions
     long long round_limit;  // variant 2: upper bound on rounds (list-scheduling bound), a guard against endless loops
     float t1, rtol, atol, dt0, safety, factor_min, factor_max, coeff1, coeff2;

@@ -131,7 +131,7 @@ def test_lv_rk4_matches_interpret_like_reference(rng, interpret_provider):
 VDP_CFG = dict(t1=20.0, rtol=1e-6, atol=1e-8, dt0=1e-3, max_steps=100_000)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 @pytest.mark.parametrize("n", [1, 33, 1000, 20_000])
 def test_vdp_safe_counts_bit_exact(n, variant):
     """SAFE shares every float operation (pow included) with the oracle, which
@@ -410,7 +410,7 @@ def test_gray_scott_temporal_blocking_bit_exact(shape, steps, fuse, persistent):
     np.testing.assert_array_equal(got_v, want_v)
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 def test_gray_scott_variants_agree(variant):
     from palladium_b200 import _native
 
