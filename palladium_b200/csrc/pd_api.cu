@@ -51,6 +51,8 @@ std::map<std::string, int64_t>& tuning() {
         {"vdp_block", 128},
         {"vdp_refill_every", 8},     // attempts between refill checks
         {"vdp_pass_limit", 1000},    // variant 3: attempts after which pass one suspends a trajectory
+        {"vdp_pass_limit2", 0},      // variant 3: cap of a second suspending pass (0 = none)
+        {"vdp_pass_limit3", 0},      // variant 3: cap of a third suspending pass (0 = none)
         {"vdp_compact_every", 16},   // variant 2: refill rounds between block-level compactions
         {"vdp_blocks_per_sm", 0},    // 0 = about 1024 resident threads per SM
         {"gbm_block", 256},
@@ -648,7 +650,11 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
                 a.bucket_of = (int32_t*)(base + 1024);
                 a.order2 = (int32_t*)(base + 1024 + 4 * per);
                 a.susp = (float*)(base + 1024 + 8 * per);
-                a.pass_limit = (int)knob("vdp_pass_limit");
+                a.pass_limits[0] = (int)knob("vdp_pass_limit");
+                a.pass_limits[1] = (int)knob("vdp_pass_limit2");
+                a.pass_limits[2] = (int)knob("vdp_pass_limit3");
+                for (int k = 1; k < 3; ++k)   // a cap that does not rise ends the list
+                    if (a.pass_limits[k] <= a.pass_limits[k - 1]) { a.pass_limits[k] = 0; if (k == 1) a.pass_limits[2] = 0; }
                 PD_CUDA_TRY(cudaMemsetAsync(base, 0, 1024, st));
                 PD_CUDA_TRY(cudaMemsetAsync(a.bucket_of, 0xFF, 4 * (size_t)per, st));
             }

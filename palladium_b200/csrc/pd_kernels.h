@@ -33,6 +33,7 @@ struct PdVdpArgs {
     // attempts and files it under a bucket of predicted remaining attempts; pass two
     // resumes the suspended states, longest predicted first.
     int pass_limit;                     // 0: never suspend
+    int pass_limits[3];                 // host side: the caps of the suspending passes, ascending, 0 = unused
     int resume;                         // lanes start from suspended states
     const unsigned long long* n_dev;    // queue length in device memory (pass two), or null for n
     unsigned long long* cursor2;        // pass two's queue head
