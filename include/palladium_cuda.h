@@ -69,7 +69,7 @@ typedef enum pd_family {
 
 /* ---- per-family parameter blocks (passed by pointer + sizeof) ------------ */
 
-/* in:  x0,y0,a,b,c,d  (N) f32.   out: x,y (N) f32.
+/* in:  x0,y0,a,b,c,d  (N) f32.   out: x,y (N) f32, or one (N,2) f32 array of (x, y) pairs.
  * The three step constants are rounded to f32 from double products exactly as
  * Python folds them: f32(0.5*dt), f32(dt), f32(dt/6). */
 typedef struct pd_lv_rk4_params {

@@ -492,6 +492,10 @@ int expected_sizes(int family, const void* params, const int64_t grid[3], std::v
     const size_t n = (size_t)grid[0];
     switch (family) {
         case PD_FAMILY_LV_RK4:
+            in->assign(6, 4 * n);
+            if (n_out_given == 1) out->assign(1, 8 * n);   // one (N, 2) array of (x, y) pairs
+            else out->assign(2, 4 * n);
+            return PD_OK;
         case PD_FAMILY_LV_RK4_DF32:
             in->assign(6, 4 * n); out->assign(2, 4 * n); return PD_OK;
         case PD_FAMILY_VDP_BS32: {
@@ -603,7 +607,14 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             PdLvArgs a;
             a.x0 = (const float*)in[0]; a.y0 = (const float*)in[1]; a.a = (const float*)in[2];
             a.b = (const float*)in[3]; a.c = (const float*)in[4]; a.d = (const float*)in[5];
-            a.xo = (float*)out[0]; a.yo = (float*)out[1];
+            a.state2_out = nullptr;
+            if (n_out == 1) {
+                if (!aligned(out[0], 8))
+                    return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output 0: (N,2) state must be 8-byte aligned");
+                a.state2_out = (float*)out[0]; a.xo = nullptr; a.yo = nullptr;
+            } else {
+                a.xo = (float*)out[0]; a.yo = (float*)out[1];
+            }
             a.n = n; a.steps = (int)p->steps;
             a.h_half = (float)(0.5 * p->dt); a.h_full = (float)p->dt;
             a.h_sixth = (float)(p->dt / 6.0);

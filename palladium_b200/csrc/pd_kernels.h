@@ -13,6 +13,7 @@
 struct PdLvArgs {
     const float *x0, *y0, *a, *b, *c, *d;
     float *xo, *yo;
+    float* state2_out;  // when set, the final state goes here as (N, 2) interleaved pairs instead of xo / yo
     int64_t n;
     int steps;
     float h_half, h_full, h_sixth;

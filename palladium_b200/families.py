@@ -108,7 +108,8 @@ class Family:
 def lv_rk4(dt: float = 0.01, steps: int = 500, pallas_fn: Callable | None = None) -> Family:
     """Fixed-step RK4 Lotka-Volterra ensemble (examples/01_ode_ensembles.py:72-91).
     Call signature: grid=(N,), six (N,) float32 inputs x0, y0, a, b, c, d,
-    two (N,) float32 outputs."""
+    two (N,) float32 outputs, or a single (N, 2) float32 output holding the
+    final (x, y) pairs."""
     return Family("lv_rk4", dict(dt=float(dt), steps=int(steps)), pallas_fn)
 
 
@@ -420,6 +421,10 @@ def trace(family: Family, call_kwargs: dict[str, Any], *args) -> KernelSpec:
         outputs = tuple(vec(n) for _ in range(2))
         blocks_in = [_per_item(n)] * 6
         blocks_out = [_per_item(n)] * 2
+        if name == "lv_rk4" and len(outs) == 1:
+            # the final state as one (N, 2) array of (x, y) pairs
+            outputs = (BlockInfo((1, 2), (n, 2), F32),)
+            blocks_out = [((1, 2), lambda i: (i, 0))]
         if name == "lv_rk4":
             params = _native.LvRk4Params(c["dt"], c["steps"])
         else:

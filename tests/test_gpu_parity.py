@@ -127,6 +127,25 @@ def test_lv_rk4_matches_interpret_like_reference(rng, interpret_provider):
     np.testing.assert_allclose(got_y, want_y, rtol=1e-3, atol=1e-5)
 
 
+@pytest.mark.parametrize("n", [1, 1000, 4099, (1 << 18) + 5])
+def test_lv_rk4_stacked_state_output(n):
+    """The final state as one (N, 2) array of (x, y) pairs equals the two-array form
+    (large n: the chunked host-buffer path)."""
+    from palladium_b200 import families, pl
+
+    ins = W.lotka_volterra_ensemble(n)
+    for mode in (SAFE, FAST):
+        x, y = H.lv_solver(n, dt=0.01, steps=60, math_mode=mode)(*ins)
+        stacked = pd.cuda_call(families.lv_rk4(0.01, 60), grid=(n,), in_specs=[H.SPEC_1] * 6,
+                               out_specs=pl.BlockSpec((1, 2), lambda i: (i, 0)),
+                               out_shape=pl.ShapeDtypeStruct((n, 2), np.float32), math_mode=mode)(*ins)
+        assert stacked.shape == (n, 2)
+        np.testing.assert_array_equal(stacked[:, 0], x)
+        np.testing.assert_array_equal(stacked[:, 1], y)
+    want = oracle.lv_rk4(*ins, dt=0.01, steps=60)
+    np.testing.assert_array_equal(x if mode is SAFE else stacked[:, 0], stacked[:, 0])
+
+
 # ------------------------------------------------------------------ adaptive BS3(2)
 VDP_CFG = dict(t1=20.0, rtol=1e-6, atol=1e-8, dt0=1e-3, max_steps=100_000)
 

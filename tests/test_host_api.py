@@ -144,7 +144,7 @@ def test_trace_rejects_malformed_requests():
         pd.cuda_call(fam, grid=(4, 4), out_shape=(H.shaped(4), H.shaped(4)))
     with pytest.raises(TraceError, match="out_shape"):
         pd.cuda_call(fam, grid=(4,), out_shape=(H.shaped(5), H.shaped(4)))
-    with pytest.raises(TraceError, match="out_shape lists 1 outputs"):
+    with pytest.raises(TraceError, match=r"out_shape\[0\] is \(4,\)"):
         pd.cuda_call(fam, grid=(4,), out_shape=H.shaped(4))
     with pytest.raises(TraceError, match="in_specs has 5 entries"):
         pd.cuda_call(fam, grid=(4,), in_specs=[spec] * 5, out_shape=(H.shaped(4), H.shaped(4)))
