@@ -42,6 +42,17 @@ LV_DT = 0.01
 LV_FLOPS_PER_TRAJ_STEP = 58  # float operations in the reference kernel's loop body
                              # (tests/golden/rk4_lotka_volterra.metal:58-258 in the reference)
 SM_COUNT = 148
+# What each math mode of the RK4 kernel is held to against the CPU oracle, and the GPU test that asserts it.
+PARITY = {
+    "safe": {"against_oracle": "bit-exact final states", "test": "tests/test_gpu_parity.py::test_rk4_named_configuration_safe_is_bit_exact"},
+    "relaxed": {"against_oracle": ">= 95 % of final states within rtol 1e-5, every state within 1e-4 (fused multiply-adds "
+                                  "round differently per operation); error against float64 no larger than the oracle's",
+                "test": "tests/test_gpu_parity.py::test_rk4_named_configuration_fast_modes"},
+    "fast": {"against_oracle": ">= 95 % of final states within rtol 1e-5, every state within 1e-4 (the kernel integrates the "
+                               "rescaled state X = c x, Y = b y); error against float64 no larger than the oracle's; "
+                               "the mode that meets rtol 1e-5 on every state is safe, timed in families.rk4_lv_safe",
+             "test": "tests/test_gpu_parity.py::test_rk4_named_configuration_fast_modes"},
+}
 FP32_LANES_PER_SM = 128
 
 
@@ -59,6 +70,8 @@ def parse_args():
     ap.add_argument("--halo", type=int, default=16, help="gray_scott on several GPUs: ghost rows per side")
     ap.add_argument("--math-mode", default="fast", choices=["safe", "relaxed", "fast"])
     ap.add_argument("--no-families", action="store_true", help="skip the short per-family measurements")
+    ap.add_argument("--no-named", action="store_true",
+                    help="skip the full-size named configurations of the other families (about 20 s)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="set a native tuning knob (pd_set_tuning), e.g. --tune vdp_variant=0")
@@ -270,7 +283,7 @@ def main():
         return float(t.item())
 
     if args.workload != "rk4_lv":
-        from palladium_b200 import bench_families
+        import bench_families
 
         bench_families.run(args, rank, local_rank, world, barrier, max_over_ranks)
         if world > 1:
@@ -372,13 +385,19 @@ def main():
             cpu_baseline["single_thread"] = {"value": one, "cores": 1, "sample": one_sample}
         if world == 1 and not args.no_families:
             try:
-                from palladium_b200 import bench_families
+                import bench_families
 
-                fam = bench_families.quick_summary()
+                fam = bench_families.quick_summary(named=not args.no_named)
                 if not args.no_cpu:
                     fam["cpu_baselines"] = cpu_family_baselines()
             except Exception as exc:  # the headline line must still be printed
                 fam = {"error": f"{type(exc).__name__}: {exc}"}
+    if world > 1 and not args.no_families:
+        # The two families whose multi-GPU form has an exchange step (the Monte Carlo's all-reduce, the
+        # stencil's halo rows), each with a check against a single-rank result; every rank takes part.
+        import bench_families
+
+        fam = bench_families.multi_gpu_summary(rank, world, barrier, max_over_ranks, args.math_mode)
 
     if rank == 0:
         line = {
@@ -387,6 +406,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "rk4_lotka_volterra", "dt": LV_DT, "rk4_steps": LV_STEPS,
                        "trajectories_per_gpu": n, "math_mode": args.math_mode, "parallelism": f"trajectory slabs x{world}",
+                       "parity": PARITY[args.math_mode],
                        "l2": "inputs + outputs are 32 B x N = 134 MB per pass, larger than the 126 MB L2; the kernel is compute-bound"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": args.steps,
             "clocks": clk, "named_config": named, "families": fam,

@@ -68,7 +68,7 @@ def _time(fn, warmup: int, iters: int) -> float:
 
 
 def _shaped(shape, dtype=np.float32):
-    from . import pl
+    from palladium_b200 import pl
 
     return pl.ShapeDtypeStruct(shape, dtype)
 
@@ -77,8 +77,8 @@ def _shaped(shape, dtype=np.float32):
 def bench_vdp(n: int, math_mode="relaxed", warmup: int = 1, iters: int = 3, fma_peak: float | None = None) -> dict:
     import torch
 
-    from . import cuda_call_jit, families
-    from . import workloads as W
+    from palladium_b200 import cuda_call_jit, families
+    from palladium_b200 import workloads as W
 
     cfg = {k: v for k, v in W.VDP_CONFIG.items() if k not in ("n", "seed")}
     call = cuda_call_jit(families.vdp_bs32(**cfg), grid=(n,),
@@ -101,8 +101,8 @@ def bench_vdp(n: int, math_mode="relaxed", warmup: int = 1, iters: int = 3, fma_
 def bench_gbm(n: int, math_mode="fast", warmup: int = 1, iters: int = 3, int_peak: float | None = None) -> dict:
     import torch
 
-    from . import cuda_call_jit, families
-    from . import workloads as W
+    from palladium_b200 import cuda_call_jit, families
+    from palladium_b200 import workloads as W
 
     cfg = {k: v for k, v in W.GBM_CONFIG.items() if k not in ("n", "seed")}
     call = cuda_call_jit(families.gbm_threefry(output="terminal", **cfg), grid=(n,),
@@ -134,7 +134,7 @@ def bench_gbm(n: int, math_mode="fast", warmup: int = 1, iters: int = 3, int_pea
 def bench_gbm_pcg(n: int, math_mode="fast", warmup: int = 1, iters: int = 3) -> dict:
     """The reference's hand-written variant (pcg_hash), at its own constants
     (examples/03_sde_montecarlo.py:30-32)."""
-    from . import cuda_call_jit, families
+    from palladium_b200 import cuda_call_jit, families
 
     call = cuda_call_jit(families.gbm_pcg(), grid=(n,), out_shape=(_shaped((n,)), _shaped((2,), np.float64)),
                          math_mode=math_mode)
@@ -151,8 +151,8 @@ def bench_gbm_pcg(n: int, math_mode="fast", warmup: int = 1, iters: int = 3) -> 
 def bench_gray_scott(size: int, steps: int, math_mode="fast", warmup: int = 1, iters: int = 3) -> dict:
     import torch
 
-    from . import cuda_call_jit, families
-    from . import workloads as W
+    from palladium_b200 import cuda_call_jit, families
+    from palladium_b200 import workloads as W
 
     cfg = {k: v for k, v in W.GRAY_SCOTT_CONFIG.items() if k not in ("steps", "size", "seed")}
     call = cuda_call_jit(families.gray_scott(steps=steps, **cfg), grid=(size, size),
@@ -172,8 +172,8 @@ def bench_gray_scott(size: int, steps: int, math_mode="fast", warmup: int = 1, i
 def bench_kepler(n: int, steps: int, warmup: int = 1, iters: int = 2, fma_peak: float | None = None) -> dict:
     import torch
 
-    from . import cuda_call_jit, families
-    from . import workloads as W
+    from palladium_b200 import cuda_call_jit, families
+    from palladium_b200 import workloads as W
 
     call = cuda_call_jit(families.kepler_rk4_df32(dt=W.KEPLER_CONFIG["dt"], gm=1.0, steps=steps), grid=(n,),
                          out_shape=tuple(_shaped((n,)) for _ in range(8)), math_mode="safe")
@@ -191,8 +191,8 @@ def bench_kepler(n: int, steps: int, warmup: int = 1, iters: int = 2, fma_peak: 
 def bench_lv_df32(n: int, steps: int, warmup: int = 1, iters: int = 3, fma_peak: float | None = None) -> dict:
     import torch
 
-    from . import cuda_call_jit, families
-    from . import workloads as W
+    from palladium_b200 import cuda_call_jit, families
+    from palladium_b200 import workloads as W
 
     call = cuda_call_jit(families.lv_rk4_df32(0.01, steps), grid=(n,), out_shape=(_shaped((n,)), _shaped((n,))),
                          math_mode="safe")
@@ -219,8 +219,8 @@ def bench_custom_ode(n: int, steps: int, math_mode: str = "fast", rhs: str = CUS
     hand-written family on the same inputs."""
     import torch
 
-    from . import cuda_call_jit, families
-    from . import workloads as W
+    from palladium_b200 import cuda_call_jit, families
+    from palladium_b200 import workloads as W
 
     out_shape = (_shaped((n,)), _shaped((n,)))
     custom = cuda_call_jit(families.custom_ode(rhs, 2, 4, dt=0.01, steps=steps), grid=(n,), out_shape=out_shape,
@@ -238,9 +238,10 @@ def bench_custom_ode(n: int, steps: int, math_mode: str = "fast", rhs: str = CUS
     return res
 
 
-def quick_summary() -> dict:
-    """Each family once, at a reduced size that finishes in a few seconds."""
-    from . import _native
+def quick_summary(named: bool = True) -> dict:
+    """Each family once at a reduced size that finishes in a few seconds, the headline kernel under the
+    other two math modes, and (named=True) every benchmark configuration at its full named size."""
+    from palladium_b200 import _native
 
     fma_peak = _native.measure_fp32_fma_peak()
     int_peak = _native.measure_int32_alu_peak()
@@ -253,6 +254,9 @@ def quick_summary() -> dict:
     out["kepler_df32"] = bench_kepler(1 << 20, 100, fma_peak=fma_peak)
     out["lv_df32"] = bench_lv_df32(1 << 20, 100, fma_peak=fma_peak)
     out["custom_ode_lv"] = bench_custom_ode(1 << 22, 1000, "fast", fma_peak=fma_peak)
+    out.update(named_rk4_modes(fma_peak))
+    if named:
+        out.update(named_configs(fma_peak, int_peak))
     return out
 
 
@@ -261,8 +265,8 @@ def full_configs(fma_peak: float, int_peak: float) -> dict:
     (`bench.py --workload full`): wall time of the whole job on the device."""
     import torch
 
-    from . import cuda_call_jit, families
-    from . import workloads as W
+    from palladium_b200 import cuda_call_jit, families
+    from palladium_b200 import workloads as W
 
     out = {"metric": "full_configurations", "value": None, "unit": "s", "scaling": "weak", "ms_per_step": None,
            "config": {"workload": "every benchmark configuration at full size, one GPU"}}
@@ -296,12 +300,357 @@ def full_configs(fma_peak: float, int_peak: float) -> dict:
     return out
 
 
+# ----------------------------------------------------------------------------- the named configurations
+# float64 RK4 of the two-body problem, one thread per orbit: the truth the df32
+# result is measured against (examples/05_df32_precision.py:95-109 does the same
+# for its system in NumPy).  A caller-written kernel, compiled at run time.
+KEPLER_F64_SOURCE = r"""
+struct S4 { double x, y, vx, vy; };
+__device__ __forceinline__ S4 kep_f(S4 s, double gm) {
+    const double r2 = s.x * s.x + s.y * s.y;
+    const double w = gm / (r2 * sqrt(r2));
+    S4 k; k.x = s.vx; k.y = s.vy; k.vx = -s.x * w; k.vy = -s.y * w; return k;
+}
+__device__ __forceinline__ S4 kep_adv(S4 s, S4 k, double h) {
+    S4 r; r.x = s.x + h * k.x; r.y = s.y + h * k.y; r.vx = s.vx + h * k.vx; r.vy = s.vy + h * k.vy; return r;
+}
+extern "C" __global__ void kepler_rk4_f64(const double* state, const double* c, double* out,
+                                          long long gx, long long gy, long long gz) {
+    const long long i = PD_THREAD_X;
+    if (i >= gx) return;
+    const double dt = c[0], gm = c[1];
+    const long long steps = (long long)c[2];
+    S4 s; s.x = state[4 * i]; s.y = state[4 * i + 1]; s.vx = state[4 * i + 2]; s.vy = state[4 * i + 3];
+    for (long long it = 0; it < steps; ++it) {
+        const S4 k1 = kep_f(s, gm);
+        const S4 k2 = kep_f(kep_adv(s, k1, 0.5 * dt), gm);
+        const S4 k3 = kep_f(kep_adv(s, k2, 0.5 * dt), gm);
+        const S4 k4 = kep_f(kep_adv(s, k3, dt), gm);
+        S4 sum;
+        sum.x = k1.x + 2.0 * k2.x + 2.0 * k3.x + k4.x;    sum.y = k1.y + 2.0 * k2.y + 2.0 * k3.y + k4.y;
+        sum.vx = k1.vx + 2.0 * k2.vx + 2.0 * k3.vx + k4.vx; sum.vy = k1.vy + 2.0 * k2.vy + 2.0 * k3.vy + k4.vy;
+        s = kep_adv(s, sum, dt / 6.0);
+    }
+    out[4 * i] = s.x; out[4 * i + 1] = s.y; out[4 * i + 2] = s.vx; out[4 * i + 3] = s.vy;
+}
+"""
+
+
+def _wall(fn) -> float:
+    import torch
+
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    fn()
+    torch.cuda.synchronize()
+    return time.perf_counter() - t0
+
+
+def named_rk4_modes(fma_peak: float, n: int = 1 << 22, steps: int = 1000) -> dict:
+    """The headline kernel under SAFE and RELAXED beside the timed FAST mode."""
+    import torch
+
+    from palladium_b200 import cuda_call_jit, families
+    from palladium_b200 import workloads as W
+
+    dev = [torch.from_numpy(a).cuda() for a in W.lotka_volterra_ensemble(n)]
+    out = {}
+    for mode, parity in (("safe", "bit-exact against the oracle"),
+                         ("relaxed", ">= 95 % of states within rtol 1e-5 of the oracle, all within 1e-4")):
+        call = cuda_call_jit(families.lv_rk4(0.01, steps), grid=(n,), out_shape=(_shaped((n,)), _shaped((n,))),
+                             math_mode=mode)
+        ms = _time(lambda: call(*dev), 2, 5)
+        out[f"rk4_lv_{mode}"] = {"trajectories": n, "rk4_steps": steps, "math_mode": mode, "ms": ms,
+                                 "trajectory_steps_per_s": float(n) * steps / (ms * 1e-3),
+                                 "frac_of_fp32_peak": float(n) * steps * 58 / (ms * 1e-3) / fma_peak, "parity": parity}
+    return out
+
+
+def named_configs(fma_peak: float, int_peak: float) -> dict:
+    """Every other benchmark configuration at its full named size on one GPU:
+    device-resident time, roofline fraction and the same job end to end from
+    host arrays (upload, run, download inside the timed region)."""
+    import torch
+
+    from palladium_b200 import cuda_call_jit, families
+    from palladium_b200 import workloads as W
+
+    out = {}
+    # ---- adaptive BS3(2), 1 000 000 Van der Pol oscillators -------------------------------------
+    cfg = {k: v for k, v in W.VDP_CONFIG.items() if k not in ("n", "seed")}
+    n = W.VDP_CONFIG["n"]
+    host = W.van_der_pol_ensemble(n)
+    pinned = [torch.from_numpy(a).pin_memory().numpy() for a in host]
+    for mode in ("safe", "relaxed"):
+        r = bench_vdp(n, mode, warmup=1, iters=2, fma_peak=fma_peak)
+        call = cuda_call_jit(families.vdp_bs32(**cfg), grid=(n,),
+                             out_shape=(_shaped((n, 2)), _shaped((n,), np.int32), _shaped((n,), np.int32)),
+                             math_mode=mode)
+        call(*pinned)
+        sec = _wall(lambda: call(*pinned))
+        r["e2e"] = {"seconds": sec, "attempts_per_s": r["attempts"] / sec, "h2d_bytes": 12 * n, "d2h_bytes": 16 * n,
+                    "path": "cuda_call_jit(host arrays) -> pd_dispatch_host"}
+        out[f"vdp_named_{mode}"] = r
+    # ---- GBM, 2^26 paths ------------------------------------------------------------------------
+    n = W.GBM_CONFIG["n"]
+    r = bench_gbm(n, "fast", warmup=1, iters=2, int_peak=int_peak)
+    gcfg = {k: v for k, v in W.GBM_CONFIG.items() if k not in ("n", "seed")}
+    call = cuda_call_jit(families.gbm_threefry(output="terminal", **gcfg), grid=(n,),
+                         out_shape=(_shaped((n,)), _shaped((2,), np.float64)), math_mode="fast")
+    key = W.gbm_key(0)
+    call(key)
+    sec = _wall(lambda: call(key))
+    r["e2e"] = {"seconds": sec, "path_steps_per_s": float(n) * gcfg["steps"] / sec, "h2d_bytes": 8,
+                "d2h_bytes": 4 * n + 16, "path": "cuda_call_jit(host key) -> pd_dispatch_host, per-path prices downloaded"}
+    out["gbm_named"] = r
+    # ---- Gray-Scott 8192^2, 10 000 steps ---------------------------------------------------------
+    size, steps = W.GRAY_SCOTT_CONFIG["size"], W.GRAY_SCOTT_CONFIG["steps"]
+    gs = {k: v_ for k, v_ in W.GRAY_SCOTT_CONFIG.items() if k not in ("steps", "size", "seed")}
+    call = cuda_call_jit(families.gray_scott(steps=steps, **gs), grid=(size, size),
+                         out_shape=(_shaped((size, size)), _shaped((size, size))), math_mode="fast")
+    u0, v0 = W.gray_scott_initial_state(size)
+    hu, hv = torch.from_numpy(u0).pin_memory(), torch.from_numpy(v0).pin_memory()
+    res = {}
+
+    def job():
+        u, v = hu.cuda(non_blocking=True), hv.cuda(non_blocking=True)
+        uo, vo = call(u, v)
+        res["u"], res["v"] = uo.cpu(), vo.cpu()
+
+    u, v = hu.cuda(), hv.cuda()
+    warm = cuda_call_jit(families.gray_scott(steps=8, **gs), grid=(size, size),
+                         out_shape=(_shaped((size, size)), _shaped((size, size))), math_mode="fast")
+    warm(u, v)                       # same grid: kernel attributes set and the ping-pong scratch allocated
+    ms = _time(lambda: call(u, v), 0, 1)
+    e2e_sec = _wall(job)
+    peak, note = _hbm_peak_gbs()
+    cell_steps = float(size) * size * steps
+    gbs = cell_steps * GS_BYTES_PER_CELL_STEP / (ms * 1e-3) / 1e9
+    ru = res["u"]
+    out["gray_scott_named"] = {
+        "workload": "Gray-Scott 8192 x 8192 periodic, 10 000 steps, 64 seeded patches + noise", "size": size, "steps": steps,
+        "math_mode": "fast", "seconds": ms / 1e3, "us_per_step": ms * 1e3 / steps,
+        "cell_steps_per_s": cell_steps / (ms * 1e-3), "algorithmic_gbs": gbs, "frac_of_hbm_peak": gbs / peak,
+        "peak_note": note, "launches": "one pd_launch call issues every fused launch back to back on the stream",
+        "u_min": float(ru.min()), "u_max": float(ru.max()), "v_max": float(res["v"].max()),
+        "finite": bool(torch.isfinite(ru).all()),
+        "e2e": {"seconds": e2e_sec, "cell_steps_per_s": cell_steps / e2e_sec, "h2d_bytes": 8 * size * size,
+                "d2h_bytes": 8 * size * size, "path": "pinned host fields uploaded, cuda_call_jit on device tensors, fields downloaded"}}
+    del u, v, res, ru
+    # ---- df32 Kepler, 1 000 000 orbits x 100 000 steps --------------------------------------------
+    kc = W.KEPLER_CONFIG
+    n, chunk = kc["n"], 1000
+    state64, pairs = W.kepler_ensemble(n)
+    call = cuda_call_jit(families.kepler_rk4_df32(dt=kc["dt"], gm=kc["gm"], steps=chunk), grid=(n,),
+                         out_shape=tuple(_shaped((n,)) for _ in range(8)), math_mode="safe")
+    pinned = [torch.from_numpy(a).pin_memory() for a in pairs]
+    got = {}
+
+    def kepler_job():
+        dev = [t.cuda(non_blocking=True) for t in pinned]
+        for _ in range(kc["steps"] // chunk):
+            dev = list(call(*dev))
+        got["pairs"] = [d.cpu().numpy() for d in dev]
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dev = [t.cuda() for t in pinned]
+    dev = list(call(*dev))          # warm-up launch (1000 steps), not part of the job
+    torch.cuda.synchronize()
+    dev = [t.cuda() for t in pinned]
+    e0.record()
+    for _ in range(kc["steps"] // chunk):
+        dev = list(call(*dev))
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / 1e3
+    del dev
+    e2e_sec = _wall(kepler_job)
+    got64 = np.stack([W.join_df32(got["pairs"][2 * i], got["pairs"][2 * i + 1]) for i in range(4)], axis=1)
+    # float64 truth on a subset of the same orbits, computed on the GPU by a caller-written kernel
+    m = 1 << 14
+    truth_call = cuda_call_jit(families.source_kernel(KEPLER_F64_SOURCE, "kepler_rk4_f64"), grid=(m,),
+                               out_shape=_shaped((m, 4), np.float64), math_mode="safe")
+    consts = torch.tensor([kc["dt"], kc["gm"], float(kc["steps"])], dtype=torch.float64, device="cuda")
+    truth = truth_call(torch.from_numpy(np.ascontiguousarray(state64[:m])).cuda(), consts).cpu().numpy()
+    err = np.hypot(got64[:m, 0] - truth[:, 0], got64[:m, 1] - truth[:, 1])
+    e_start, e_end = W.kepler_energy(state64), W.kepler_energy(got64)
+    drift = np.abs(e_end - e_start) / np.abs(e_start)
+    drift_truth = np.abs(W.kepler_energy(truth) - e_start[:m]) / np.abs(e_start[:m])
+    ts = float(n) * kc["steps"]
+    out["kepler_named"] = {
+        "workload": "df32 RK4 Kepler orbits, SAFE", "trajectories": n, "steps": kc["steps"], "launches": kc["steps"] // chunk,
+        "seconds": sec, "trajectory_steps_per_s": ts / sec, "flops_per_trajectory_step": DF32_KEPLER_FLOPS,
+        "frac_of_fp32_peak": ts * DF32_KEPLER_FLOPS / sec / fma_peak,
+        "final_position_error_vs_float64": {"subset": m, "max": float(err.max()), "median": float(np.median(err)),
+                                            "truth": "float64 RK4 of the same orbits, a run-time compiled kernel on the GPU"},
+        "relative_energy_drift": {"max_all_orbits": float(drift.max()), "median_all_orbits": float(np.median(drift)),
+                                  "max_float64_truth_subset": float(drift_truth.max())},
+        "e2e": {"seconds": e2e_sec, "trajectory_steps_per_s": ts / e2e_sec, "h2d_bytes": 32 * n, "d2h_bytes": 32 * n,
+                "path": "pinned host state uploaded, 100 cuda_call_jit launches on device tensors, state downloaded"}}
+    return out
+
+
+# ----------------------------------------------------------------------------- several GPUs
+def _black_scholes(cfg: dict) -> float:
+    from math import erf, exp, log, sqrt
+
+    d1 = (log(cfg["s0"] / cfg["strike"]) + (cfg["r"] + cfg["sigma"] ** 2 / 2) * cfg["t"]) / (cfg["sigma"] * sqrt(cfg["t"]))
+    d2 = d1 - cfg["sigma"] * sqrt(cfg["t"])
+    cdf = lambda x: 0.5 * (1.0 + erf(x / sqrt(2.0)))  # noqa: E731
+    return cfg["s0"] * cdf(d1) - cfg["strike"] * exp(-cfg["r"] * cfg["t"]) * cdf(d2)
+
+
+def _gather_rows(local, world: int):
+    """All ranks' equally sized first-axis shares, concatenated in rank order (on every rank)."""
+    import torch
+    import torch.distributed as dist
+
+    full = torch.empty((local.shape[0] * world, *local.shape[1:]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(full, local.contiguous())
+    return full
+
+
+def multi_gpu_gbm(rank: int, world: int, barrier, max_over_ranks, math_mode: str = "fast", paths_per_gpu: int = 1 << 24,
+                  iters: int = 3) -> dict:
+    """The Monte Carlo on `world` GPUs: path slabs keyed by global path index, one
+    all-reduce of two float64 sums per pass (examples/03_sde_montecarlo.py:137-146
+    prices from one device's payoffs).  Checked in the same run: a 2^20-path case
+    priced by all ranks together against rank 0 pricing it alone."""
+    import torch
+
+    from palladium_b200 import _native, sharded
+    from palladium_b200 import workloads as W
+
+    cfg = {k: v for k, v in W.GBM_CONFIG.items() if k not in ("n", "seed")}
+    key = W.gbm_key(0)
+    # ---- the check: every rank's paths and the all-reduced sums against one rank alone ----
+    n_check = 1 << 20
+    together = sharded.gbm_monte_carlo(key, n_check, cfg, math_mode=math_mode)
+    everyone = _gather_rows(together.local_output, world) if n_check % world == 0 else None
+    check = None
+    if rank == 0:
+        alone_out, alone_sums = sharded._cuda_gbm_paths(key, 0, n_check, cfg, math_mode, "terminal")
+        a1, a2 = (float(x) for x in alone_sums.cpu())
+        check = {
+            "paths": n_check,
+            # payoffs are multiples of 2^-17 (s >= strike = 100), so their float64 sum is exact in any order
+            "sum_payoff_equal_single_rank": together.sums[0] == a1,
+            "sum_payoff_sq_rel_diff": abs(together.sums[1] - a2) / a2 if a2 else 0.0,
+            "per_path_outputs_equal_single_rank": bool(torch.equal(everyone, alone_out)) if everyone is not None else None,
+        }
+        check["sums_equal_single_rank"] = bool(check["sum_payoff_equal_single_rank"]
+                                               and check["sum_payoff_sq_rel_diff"] < 1e-13
+                                               and check["per_path_outputs_equal_single_rank"] is not False)
+    # ---- throughput ----
+    n_total = paths_per_gpu * world
+    res = sharded.gbm_monte_carlo(key, n_total, cfg, math_mode=math_mode)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        res = sharded.gbm_monte_carlo(key, n_total, cfg, math_mode=math_mode)
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / iters
+    exact = _black_scholes(cfg)
+    value = float(n_total) * cfg["steps"] / (ms * 1e-3)
+    int_peak = _native.measure_int32_alu_peak()
+    return {"workload": "GBM Monte Carlo, Threefry in-kernel, path slabs by global path index", "n_gpus": world,
+            "paths_total": n_total, "paths_per_gpu": paths_per_gpu, "steps": cfg["steps"], "math_mode": math_mode,
+            "collective": "one NCCL all_reduce of 2 float64 per pass", "ms": ms, "path_steps_per_s": value,
+            "price": res.price, "stderr": res.stderr, "black_scholes": exact,
+            "sigmas_from_black_scholes": abs(res.price - exact) / res.stderr if res.stderr else None,
+            "frac_of_int32_peak_per_gpu": value / world * GBM_INT_OPS_PER_PATH_STEP / int_peak, "check": check,
+            "sums_equal_single_rank": check["sums_equal_single_rank"] if check else None}
+
+
+def multi_gpu_gray_scott(rank: int, world: int, barrier, max_over_ranks, math_mode: str = "fast", cols: int = 16384,
+                         halo: int = 16, steps_per_pass: int = 64, iters: int = 3) -> dict:
+    """The stencil on `world` GPUs: row slabs on a periodic ring, boundary rows
+    stored into the neighbours' ghost rows by the compute kernel (peer stores
+    over NVLink, no multicast, nothing waits inside a kernel).  16384 x 16384 on 8
+    GPUs (2048 rows per GPU); 8192 rows x 16384 columns per GPU otherwise.
+    Checked in the same run: a 1024 x 16384 grid advanced 32 steps under SAFE by
+    the slabs against rank 0 advancing the whole grid alone."""
+    import torch
+
+    from palladium_b200 import cuda_call_jit, families, sharded
+    from palladium_b200 import workloads as W
+
+    cfg = {k: v_ for k, v_ in W.GRAY_SCOTT_CONFIG.items() if k not in ("steps", "size", "seed")}
+    # ---- the check ----
+    rows_c, steps_c = 1024, 32
+    rng = np.random.default_rng(11)
+    u0 = (0.5 + 0.5 * rng.random((rows_c, cols), dtype=np.float32))
+    v0 = (0.25 * rng.random((rows_c, cols), dtype=np.float32))
+    lo, hi = sharded.partition(rows_c, world, rank)
+    slab = sharded.GrayScottSlab(torch.from_numpy(u0[lo:hi]).cuda(), torch.from_numpy(v0[lo:hi]).cuda(), rows_c,
+                                 halo=halo, constants=cfg, math_mode="safe", push=True)
+    slab.advance(steps_c)
+    su, sv = (t.clone() for t in slab.owned())
+    pushes, exchanges = slab.pushes, slab.exchanges
+    slab.close()
+    equal = None
+    if rows_c % world == 0:
+        full_u, full_v = _gather_rows(su, world), _gather_rows(sv, world)
+        if rank == 0:
+            whole = cuda_call_jit(families.gray_scott(steps=steps_c, **cfg), grid=(rows_c, cols),
+                                  out_shape=(_shaped((rows_c, cols)), _shaped((rows_c, cols))), math_mode="safe")
+            wu, wv = whole(torch.from_numpy(u0).cuda(), torch.from_numpy(v0).cuda())
+            equal = bool(torch.equal(full_u, wu) and torch.equal(full_v, wv))
+    # ---- throughput ----
+    rows_per_gpu = 2048 if world >= 8 else 8192
+    rows_total = rows_per_gpu * world
+    u = torch.rand((rows_per_gpu, cols), device="cuda") * 0.5 + 0.5
+    v = torch.rand((rows_per_gpu, cols), device="cuda") * 0.25
+    slab = sharded.GrayScottSlab(u, v, rows_total, halo=halo, constants=cfg, math_mode=math_mode, push=True)
+    del u, v
+    for _ in range(2):
+        slab.advance(steps_per_pass)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        slab.advance(steps_per_pass)
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / iters
+    finite = bool(torch.isfinite(slab.owned()[0]).all())
+    slab.close()
+    cell_steps = float(rows_total) * cols * steps_per_pass
+    value = cell_steps / (ms * 1e-3)
+    peak, note = _hbm_peak_gbs()
+    gbs = value / world * GS_BYTES_PER_CELL_STEP / 1e9
+    return {"workload": "Gray-Scott periodic 5-point stencil, row slabs", "n_gpus": world, "rows": rows_total,
+            "cols": cols, "rows_per_gpu": rows_per_gpu, "halo": halo, "math_mode": math_mode,
+            "exchange": f"boundary rows stored into the neighbours' ghost rows by the compute kernel every {halo} steps "
+                        "(peer stores over NVLink), one 1-element all_reduce per exchange orders the calls",
+            "steps_per_pass": steps_per_pass, "ms_per_pass": ms, "us_per_step": ms * 1e3 / steps_per_pass,
+            "cell_steps_per_s": value, "algorithmic_gbs_per_gpu": gbs, "hbm_peak_gbs": peak,
+            "frac_of_hbm_peak_per_gpu": gbs / peak, "peak_note": note, "finite": finite,
+            "check": {"rows": rows_c, "cols": cols, "steps": steps_c, "math_mode": "safe", "pushes": pushes,
+                      "point_to_point_exchanges": exchanges},
+            "slab_equals_single_gpu": equal}
+
+
+def multi_gpu_summary(rank: int, world: int, barrier, max_over_ranks, math_mode: str = "fast") -> dict:
+    """The two families whose multi-GPU form has an exchange step, run by every
+    rank of the job; the dict is meaningful on rank 0."""
+    out = {}
+    for name, fn in (("gbm", multi_gpu_gbm), ("gray_scott", multi_gpu_gray_scott)):
+        try:
+            out[name] = fn(rank, world, barrier, max_over_ranks, math_mode)
+        except Exception as exc:   # every rank takes the same path: the failure is reported, the headline still prints
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"}
+    return out
+
+
 # ----------------------------------------------------------------------------- as the main workload
 def run(args, rank: int, local_rank: int, world: int, barrier, max_over_ranks) -> None:
     import torch
 
-    from . import _native, sharded
-    from . import workloads as W
+    from palladium_b200 import _native, sharded
+    from palladium_b200 import workloads as W
 
     fma_peak = _native.measure_fp32_fma_peak()
     int_peak = _native.measure_int32_alu_peak()

@@ -316,6 +316,16 @@ PD_API int pd_explain(int family, const void* params, size_t params_bytes, int m
 PD_API int pd_set_tuning(const char* key, int64_t value);
 PD_API int pd_get_tuning(const char* key, int64_t* value);
 
+/* The same knobs, overridden for the calling thread only: calls made by this
+ * thread see `value`, every other thread keeps the process-wide setting.  This
+ * is how one call picks a kernel variant without changing what concurrent
+ * callers run (the reference has no counterpart: its only per-call choices are
+ * math_mode and threadgroup, src/palladium/__init__.py:222-226).
+ * pd_clear_thread_tuning(NULL) drops all of the thread's overrides.
+ * pd_get_tuning reports the value the calling thread would use. */
+PD_API int pd_set_thread_tuning(const char* key, int64_t value);
+PD_API int pd_clear_thread_tuning(const char* key);
+
 /* Roofline denominators measured on the current device: a chain of dependent
  * FP32 FMAs (2 flops each) and a chain of 32-bit integer add/xor/funnel-shift
  * operations, both with enough independent chains per thread to saturate issue.

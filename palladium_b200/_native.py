@@ -45,6 +45,8 @@ EXPORTED_SYMBOLS = (
     "pd_explain",
     "pd_set_tuning",
     "pd_get_tuning",
+    "pd_set_thread_tuning",
+    "pd_clear_thread_tuning",
     "pd_measure_fp32_fma_peak",
     "pd_measure_int32_alu_peak",
     "pd_last_kernel_ms",
@@ -166,6 +168,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pd_set_tuning.argtypes = [cp, _i64]
     lib.pd_get_tuning.restype = ci
     lib.pd_get_tuning.argtypes = [cp, i64p]
+    lib.pd_set_thread_tuning.restype = ci
+    lib.pd_set_thread_tuning.argtypes = [cp, _i64]
+    lib.pd_clear_thread_tuning.restype = ci
+    lib.pd_clear_thread_tuning.argtypes = [cp]
     lib.pd_measure_fp32_fma_peak.restype = ci
     lib.pd_measure_fp32_fma_peak.argtypes = [ctypes.POINTER(_dbl), cp, sz]
     lib.pd_measure_int32_alu_peak.restype = ci
@@ -303,6 +309,29 @@ def get_tuning(key: str) -> int:
     if library().pd_get_tuning(key.encode(), ctypes.byref(out)):
         raise KeyError(f"unknown tuning key {key!r}")
     return int(out.value)
+
+
+class thread_tuning:
+    """Context manager: tuning knobs overridden for the calling thread only
+    (pd_set_thread_tuning), restored on exit.  `with thread_tuning(gs_variant=1): call(...)`
+    picks a kernel variant for that call without touching other threads' calls."""
+
+    def __init__(self, **knobs: int):
+        self.knobs = knobs
+
+    def __enter__(self):
+        lib = library()
+        for key, value in self.knobs.items():
+            if lib.pd_set_thread_tuning(key.encode(), int(value)):
+                self.__exit__()
+                raise KeyError(f"unknown tuning key {key!r}")
+        return self
+
+    def __exit__(self, *exc):
+        lib = library()
+        for key in self.knobs:
+            lib.pd_clear_thread_tuning(key.encode())
+        return False
 
 
 def device_count() -> int:

@@ -13,6 +13,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <string>
@@ -40,36 +41,59 @@ int fail(int code, char* err, size_t cap, const char* fmt, ...) {
     } while (0)
 
 // ---------------------------------------------------------------------------
-// tuning knobs
+// tuning knobs: a fixed table of integers.  Reading one on the launch path is a
+// relaxed atomic load (no lock, no string look-up); names are resolved only by
+// the setters.  A thread may override a knob for its own calls
+// (pd_set_thread_tuning), so a caller can pick a kernel variant without
+// changing what other threads of the process run.
 // ---------------------------------------------------------------------------
-std::mutex g_tuning_mutex;
-std::map<std::string, int64_t>& tuning() {
-    static std::map<std::string, int64_t> t = {
-        {"lv_items_per_thread", 0},  // 0 = choose from N and alignment
-        {"lv_block", 0},             // 0 = choose from N
-        {"vdp_variant", 2},          // 0 direct, 1 lane refill, 2 refill + tail compaction, 3 two passes, longest predicted first
-        {"vdp_block", 128},
-        {"vdp_refill_every", 8},     // attempts between refill checks
-        {"vdp_pass_limit", 1000},    // variant 3: attempts after which pass one suspends a trajectory
-        {"vdp_pass_limit2", 0},      // variant 3: cap of a second suspending pass (0 = none)
-        {"vdp_pass_limit3", 0},      // variant 3: cap of a third suspending pass (0 = none)
-        {"vdp_compact_every", 16},   // variant 2: refill rounds between block-level compactions
-        {"vdp_blocks_per_sm", 0},    // 0 = about 1024 resident threads per SM
-        {"gbm_block", 256},
-        {"gbm_blocks_per_sm", 0},
-        {"gs_variant", -1},          // -1 = best for the shape; 0 per cell, 1 vec4 (one step), 2 temporal blocking
-        {"gs_fuse", 4},              // steps fused per launch by variant 2 (2..4)
-        {"gs_persistent", 0},        // variant 2: one tile per block (0, faster at K = 4) or persistent blocks with cp.async prefetch (1)
-        {"df32_block", 128},
-        {"host_streams", 3},         // streams the chunks of a host-buffer call rotate over (1..8)
-        {"host_chunks", -1},         // chunks a large host-buffer call is cut into (-1 = by size, 0 = ramped sizes)
-        {"time_kernels", 0},
-    };
-    return t;
+#define PD_KNOBS(X)                                                                                              \
+    X(lv_items_per_thread, 0)  /* 0 = choose from N and alignment */                                            \
+    X(lv_block, 0)             /* 0 = choose from N */                                                          \
+    X(vdp_variant, 2)          /* 0 direct, 1 lane refill, 2 refill + tail compaction, 3 two passes */           \
+    X(vdp_block, 128)                                                                                            \
+    X(vdp_refill_every, 8)     /* attempts between refill checks */                                             \
+    X(vdp_pass_limit, 1000)    /* variant 3: attempts after which pass one suspends a trajectory */             \
+    X(vdp_pass_limit2, 0)      /* variant 3: cap of a second suspending pass (0 = none) */                      \
+    X(vdp_pass_limit3, 0)      /* variant 3: cap of a third suspending pass (0 = none) */                       \
+    X(vdp_compact_every, 16)   /* variant 2: refill rounds between block-level compactions */                   \
+    X(vdp_blocks_per_sm, 0)    /* 0 = about 1024 resident threads per SM */                                     \
+    X(gbm_block, 256)                                                                                            \
+    X(gbm_blocks_per_sm, 0)                                                                                      \
+    X(gs_variant, -1)          /* -1 = best for the shape; 0 per cell, 1 vec4 (one step), 2 temporal blocking */ \
+    X(gs_fuse, 0)              /* steps fused per launch by variant 2; 0 = the kernel's default */              \
+    X(gs_persistent, 0)        /* variant 2: 0 one tile per block, 1 persistent blocks with cp.async prefetch, 2 TMA-fed */ \
+    X(df32_block, 128)                                                                                           \
+    X(host_streams, 3)         /* streams the chunks of a host-buffer call rotate over (1..8) */                \
+    X(host_chunks, -1)         /* chunks of a large host-buffer call (-1 = by size, 0 = ramped sizes) */        \
+    X(time_kernels, 0)
+
+enum Knob {
+#define X(name, def) K_##name,
+    PD_KNOBS(X)
+#undef X
+    K_COUNT
+};
+const char* const kKnobNames[K_COUNT] = {
+#define X(name, def) #name,
+    PD_KNOBS(X)
+#undef X
+};
+std::atomic<int64_t> g_knobs[K_COUNT] = {
+#define X(name, def) {def},
+    PD_KNOBS(X)
+#undef X
+};
+struct ThreadKnobs { bool set[K_COUNT] = {}; int64_t value[K_COUNT] = {}; };
+thread_local ThreadKnobs t_knobs;
+
+int knob_index(const char* key) {
+    for (int i = 0; i < K_COUNT; ++i)
+        if (strcmp(kKnobNames[i], key) == 0) return i;
+    return -1;
 }
-int64_t knob(const char* key) {
-    std::lock_guard<std::mutex> lock(g_tuning_mutex);
-    return tuning()[key];
+inline int64_t knob(Knob k) {
+    return t_knobs.set[k] ? t_knobs.value[k] : g_knobs[k].load(std::memory_order_relaxed);
 }
 
 // ---------------------------------------------------------------------------
@@ -180,7 +204,7 @@ int get_params(const void* params, size_t bytes, const P** out, const char* what
 }
 
 int lv_items_for(int64_t n, int sms, bool vec_ok) {
-    int64_t forced = knob("lv_items_per_thread");
+    int64_t forced = knob(K_lv_items_per_thread);
     if (forced == 1 || forced == 2 || forced == 4) return vec_ok ? (int)forced : 1;
     if (!vec_ok) return 1;
     // Keep at least ~2048 threads per SM before trading threads for per-thread ILP.
@@ -212,7 +236,7 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
             if (p->steps < 0 || p->steps > INT32_MAX)
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "lv_rk4: steps out of range");
             const int items = lv_items_for(n, dev.sms, vec_ok);
-            int b = req_block ? req_block : (int)knob("lv_block");
+            int b = req_block ? req_block : (int)knob(K_lv_block);
             if (!b) b = (n / items >= (int64_t)dev.sms * 2048) ? 128 : 64;
             plan->kernel_name = items == 4 ? "pd_lv_rk4_kernel<4>" : items == 2 ? "pd_lv_rk4_kernel<2>" : "pd_lv_rk4_kernel<1>";
             plan->items = items;
@@ -233,11 +257,11 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "vdp_bs32: out_layout must be 0, 1 or 2");
             if (p->error_order <= 0)
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "vdp_bs32: error_order must be positive");
-            const int variant = (int)knob("vdp_variant");
-            int b = req_block ? req_block : (int)knob("vdp_block");
+            const int variant = (int)knob(K_vdp_variant);
+            int b = req_block ? req_block : (int)knob(K_vdp_block);
             int variant_used = variant;
             // two passes make sense only when a trajectory can outlast the first one
-            if (variant == 3 && p->max_steps <= knob("vdp_pass_limit")) variant_used = 2;
+            if (variant == 3 && p->max_steps <= knob(K_vdp_pass_limit)) variant_used = 2;
             if (variant_used >= 2) b = 256;   // the compaction kernel's shared arrays are sized for 256 threads
             plan->variant = variant_used;
             plan->kernel = mt->kernel_ptr(family, variant);
@@ -250,7 +274,7 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 // About 1024 resident threads per SM measured best: enough warps to
                 // hide the divide / pow latencies, and few enough threads that each one
                 // integrates many trajectories, which evens out the heavy-tailed work.
-                int per_sm = (int)knob("vdp_blocks_per_sm");
+                int per_sm = (int)knob(K_vdp_blocks_per_sm);
                 if (!per_sm) {
                     per_sm = 1024 / b > 0 ? 1024 / b : 1;
                     const int occ = dev.present ? occupancy_blocks(plan->kernel, b) : 0;
@@ -343,10 +367,10 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
             if (p->path_offset < 0 || p->path_offset + n > ((int64_t)1 << 32))
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
                             "gbm_threefry: path indices must fit in 32 bits (fold_in takes a uint32)");
-            int b = req_block ? req_block : (int)knob("gbm_block");
+            int b = req_block ? req_block : (int)knob(K_gbm_block);
             plan->kernel_name = family == PD_FAMILY_GBM_PCG ? "pd_gbm_kernel<pcg>" : "pd_gbm_kernel<threefry>";
             plan->kernel = mt->kernel_ptr(family, 0);
-            int per_sm = (int)knob("gbm_blocks_per_sm");
+            int per_sm = (int)knob(K_gbm_blocks_per_sm);
             if (!per_sm) per_sm = dev.present ? occupancy_blocks(plan->kernel, b) : 0;
             if (per_sm <= 0) per_sm = 2048 / b / 2;
             int64_t g = (int64_t)dev.sms * per_sm;
@@ -377,11 +401,18 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
             const int64_t rows_alloc = p->rows + 2 * p->halo;
             if (rows_alloc * p->cols >= ((int64_t)1 << 31))
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott: more than 2^31 cells per call");
-            int variant = (int)knob("gs_variant");
+            int variant = (int)knob(K_gs_variant);
             const bool vec_shape = (p->cols % 4 == 0) && p->cols >= 128 && vec_ok;
+            // the one-thread-per-cell kernel spreads rows over the second launch dimension, 8 per block
+            if ((!vec_shape || variant == 0) && (rows_alloc + 7) / 8 > 65535)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                            "gray_scott: %lld rows of %lld columns cannot be launched (grids narrower than 128 "
+                            "columns, with a column count that is not a multiple of 4, or in unaligned buffers take at "
+                            "most 524280 rows)", (long long)rows_alloc, (long long)p->cols);
             if (variant < 0) variant = vec_shape ? (p->steps >= 2 ? 2 : 1) : 0;
             if (variant >= 1 && !vec_shape) variant = 0;
-            int fuse = (int)knob("gs_fuse");
+            int fuse = (int)knob(K_gs_fuse);
+            if (fuse == 0) fuse = 4;
             fuse = fuse < 2 ? 2 : (fuse > 4 ? 4 : fuse);
             plan->variant = variant;
             int64_t launches = p->steps;
@@ -401,7 +432,7 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 plan->grid[1] = (rows_alloc + PD_GS_TILE_ROWS - 1) / PD_GS_TILE_ROWS;
             } else {
                 const int k = p->steps < fuse ? (int)p->steps : fuse;
-                const bool persistent = knob("gs_persistent") != 0;
+                const bool persistent = knob(K_gs_persistent) != 0;
                 plan->variant = (persistent ? 20 : 10) + k;  // the kernel of the full-size launches
                 plan->kernel = mt->kernel_ptr(family, plan->variant);
                 plan->kernel_name = persistent
@@ -435,7 +466,7 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
             }
             if (steps < 0 || steps > INT32_MAX)
                 return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "df32: steps out of range");
-            int b = req_block ? req_block : (int)knob("df32_block");
+            int b = req_block ? req_block : (int)knob(K_df32_block);
             plan->block[0] = b;
             plan->grid[0] = (n + b - 1) / b;
             plan->kernel = pd_common_kernel_ptr(family);
@@ -589,7 +620,7 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
         }
     }
 
-    const bool timed = knob("time_kernels") != 0;
+    const bool timed = knob(K_time_kernels) != 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     t_last_kernel_ms = -1.0;
     if (timed) {
@@ -639,7 +670,7 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
                 if (p->out_layout == 0) a.real_out = (float*)out[5];
             }
             a.n = n; a.max_steps = (int)p->max_steps;
-            a.refill_every = (int)knob("vdp_refill_every");
+            a.refill_every = (int)knob(K_vdp_refill_every);
             if (a.refill_every < 1) a.refill_every = 1;
             a.t1 = (float)p->t1; a.rtol = (float)p->rtol; a.atol = (float)p->atol; a.dt0 = (float)p->dt0;
             a.safety = (float)p->safety; a.factor_min = (float)p->factor_min; a.factor_max = (float)p->factor_max;
@@ -661,16 +692,16 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
                 a.bucket_of = (int32_t*)(base + 1024);
                 a.order2 = (int32_t*)(base + 1024 + 4 * per);
                 a.susp = (float*)(base + 1024 + 8 * per);
-                a.pass_limits[0] = (int)knob("vdp_pass_limit");
-                a.pass_limits[1] = (int)knob("vdp_pass_limit2");
-                a.pass_limits[2] = (int)knob("vdp_pass_limit3");
+                a.pass_limits[0] = (int)knob(K_vdp_pass_limit);
+                a.pass_limits[1] = (int)knob(K_vdp_pass_limit2);
+                a.pass_limits[2] = (int)knob(K_vdp_pass_limit3);
                 for (int k = 1; k < 3; ++k)   // a cap that does not rise ends the list
                     if (a.pass_limits[k] <= a.pass_limits[k - 1]) { a.pass_limits[k] = 0; if (k == 1) a.pass_limits[2] = 0; }
                 PD_CUDA_TRY(cudaMemsetAsync(base, 0, 1024, st));
                 PD_CUDA_TRY(cudaMemsetAsync(a.bucket_of, 0xFF, 4 * (size_t)per, st));
             }
             if (plan.variant >= 2) {
-                a.compact_every = (int)knob("vdp_compact_every");
+                a.compact_every = (int)knob(K_vdp_compact_every);
                 if (a.compact_every < 1) a.compact_every = 1;
                 // list scheduling: the last lane finishes within (average load + longest job) rounds
                 const long long lanes = (long long)plan.grid[0] * b;
@@ -812,7 +843,7 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
                 a.coeff1 = (float)((p->icoeff + p->pcoeff) / (double)p->error_order);
                 a.coeff2 = (float)(-p->pcoeff / (double)p->error_order);
                 a.cursor = (unsigned long long*)scratch;
-                a.refill_every = (int)knob("vdp_refill_every");
+                a.refill_every = (int)knob(K_vdp_refill_every);
                 if (a.refill_every < 1) a.refill_every = 1;
                 PD_CUDA_TRY(cudaMemsetAsync(scratch, 0, 256, st));
             }
@@ -1012,7 +1043,7 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
         // for the kernels' best configuration.
         std::vector<int64_t> bounds;   // chunk c covers [bounds[c], bounds[c + 1])
         {
-            int64_t want_chunks = knob("host_chunks");
+            int64_t want_chunks = knob(K_host_chunks);
             if (want_chunks < 0) {
                 // about 2^17 trajectories per chunk measured best from 2^20 to 2^22 (8 / 16 / 32
                 // chunks); beyond that more, larger chunks
@@ -1040,23 +1071,33 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
             }
             bounds.push_back(n);
         }
-        int n_streams = (int)knob("host_streams");
+        int n_streams = (int)knob(K_host_streams);
         n_streams = n_streams < 1 ? 1 : (n_streams > kHostStreams ? kHostStreams : n_streams);
+        // From the first queued copy on, an error must not return before every stream has been
+        // drained: queued copies still read and write the caller's host buffers, and the call is
+        // blocking by contract.  Errors are recorded in rc and end the loops; the synchronise
+        // loop at the end always runs.
+        int rc = PD_OK;
+        auto cuda_ok = [&](cudaError_t e, const char* what) {
+            if (e == cudaSuccess) return true;
+            if (rc == PD_OK) rc = fail(PD_ERR_CUDA, err, err_cap, "%s failed: %s", what, cudaGetErrorString(e));
+            return false;
+        };
         bool any_broadcast = false;
-        for (int i = 0; i < n_in; ++i) {
+        for (int i = 0; i < n_in && rc == PD_OK; ++i) {
             if (in_item[i] == 0 && in_bytes[i]) {
-                PD_CUDA_TRY(cudaMemcpyAsync(hs.slots[i].ptr, in[i], in_bytes[i], cudaMemcpyHostToDevice, hs.streams[0]));
+                cuda_ok(cudaMemcpyAsync(hs.slots[i].ptr, in[i], in_bytes[i], cudaMemcpyHostToDevice, hs.streams[0]),
+                        "cudaMemcpyAsync (shared input)");
                 any_broadcast = true;
             }
         }
-        if (any_broadcast) {
-            PD_CUDA_TRY(cudaEventRecord(hs.broadcast_done, hs.streams[0]));
-            for (int sidx = 1; sidx < n_streams; ++sidx)
-                PD_CUDA_TRY(cudaStreamWaitEvent(hs.streams[sidx], hs.broadcast_done, 0));
+        if (any_broadcast && rc == PD_OK) {
+            cuda_ok(cudaEventRecord(hs.broadcast_done, hs.streams[0]), "cudaEventRecord");
+            for (int sidx = 1; sidx < n_streams && rc == PD_OK; ++sidx)
+                cuda_ok(cudaStreamWaitEvent(hs.streams[sidx], hs.broadcast_done, 0), "cudaStreamWaitEvent");
         }
         unsigned char local_params[256];
         memcpy(local_params, params, params_bytes);
-        int rc = PD_OK;
         int c = 0;
         std::vector<const void*> c_in(n_in);
         std::vector<void*> c_out(n_out);
@@ -1070,8 +1111,9 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
                     const size_t off = (size_t)lo * in_item[i];
                     c_in[i] = (const char*)hs.slots[i].ptr + off;
                     c_in_bytes[i] = (size_t)len * in_item[i];
-                    PD_CUDA_TRY(cudaMemcpyAsync((char*)hs.slots[i].ptr + off, (const char*)in[i] + off, c_in_bytes[i],
-                                                cudaMemcpyHostToDevice, st));
+                    if (!cuda_ok(cudaMemcpyAsync((char*)hs.slots[i].ptr + off, (const char*)in[i] + off, c_in_bytes[i],
+                                                 cudaMemcpyHostToDevice, st), "cudaMemcpyAsync (upload)"))
+                        break;
                 } else {
                     c_in[i] = hs.slots[i].ptr;
                     c_in_bytes[i] = in_bytes[i];
@@ -1087,13 +1129,14 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
                 gp.path_offset += lo;
                 memcpy(local_params, &gp, sizeof(gp));
             }
+            if (rc) break;
             const int64_t c_grid[3] = {len, grid[1], grid[2]};
             rc = launch_impl(family, local_params, params_bytes, math_mode, c_grid, block, n_in, c_in.data(),
                              c_in_bytes.data(), n_out, c_out.data(), c_out_bytes.data(), nullptr, 0, st, err, err_cap);
             if (rc) break;
-            for (int i = 0; i < n_out; ++i)
-                PD_CUDA_TRY(cudaMemcpyAsync((char*)out[i] + (size_t)lo * out_item[i], c_out[i], c_out_bytes[i],
-                                            cudaMemcpyDeviceToHost, st));
+            for (int i = 0; i < n_out && rc == PD_OK; ++i)
+                cuda_ok(cudaMemcpyAsync((char*)out[i] + (size_t)lo * out_item[i], c_out[i], c_out_bytes[i],
+                                        cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync (download)");
         }
         for (int sidx = 0; sidx < kHostStreams; ++sidx) {
             cudaError_t e = cudaStreamSynchronize(hs.streams[sidx]);
@@ -1104,18 +1147,25 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
     }
 
     // ---- one upload, one launch sequence, one download --------------------------------
-    for (int i = 0; i < n_in; ++i)
-        if (in_bytes[i]) PD_CUDA_TRY(cudaMemcpyAsync(hs.slots[i].ptr, in[i], in_bytes[i], cudaMemcpyHostToDevice, hs.stream));
-    int rc = launch_impl(family, params, params_bytes, math_mode, grid, block, n_in, d_in.data(), in_bytes, n_out,
-                         d_out.data(), out_bytes, nullptr, 0, hs.stream, err, err_cap);
-    if (rc) {
-        cudaStreamSynchronize(hs.stream);
-        return rc;
+    int rc = PD_OK;
+    for (int i = 0; i < n_in && rc == PD_OK; ++i) {
+        if (!in_bytes[i]) continue;
+        cudaError_t e = cudaMemcpyAsync(hs.slots[i].ptr, in[i], in_bytes[i], cudaMemcpyHostToDevice, hs.stream);
+        if (e != cudaSuccess) rc = fail(PD_ERR_CUDA, err, err_cap, "cudaMemcpyAsync (upload) failed: %s", cudaGetErrorString(e));
     }
-    for (int i = 0; i < n_out; ++i)
-        if (out_bytes[i]) PD_CUDA_TRY(cudaMemcpyAsync(out[i], d_out[i], out_bytes[i], cudaMemcpyDeviceToHost, hs.stream));
-    PD_CUDA_TRY(cudaStreamSynchronize(hs.stream));
-    return PD_OK;
+    if (rc == PD_OK)
+        rc = launch_impl(family, params, params_bytes, math_mode, grid, block, n_in, d_in.data(), in_bytes, n_out,
+                         d_out.data(), out_bytes, nullptr, 0, hs.stream, err, err_cap);
+    for (int i = 0; i < n_out && rc == PD_OK; ++i) {
+        if (!out_bytes[i]) continue;
+        cudaError_t e = cudaMemcpyAsync(out[i], d_out[i], out_bytes[i], cudaMemcpyDeviceToHost, hs.stream);
+        if (e != cudaSuccess) rc = fail(PD_ERR_CUDA, err, err_cap, "cudaMemcpyAsync (download) failed: %s", cudaGetErrorString(e));
+    }
+    // the call is blocking by contract: queued copies still use the caller's buffers, so drain on every path
+    cudaError_t e = cudaStreamSynchronize(hs.stream);
+    if (e != cudaSuccess && rc == PD_OK)
+        rc = fail(PD_ERR_CUDA, err, err_cap, "cudaStreamSynchronize failed: %s", cudaGetErrorString(e));
+    return rc;
 }
 
 int pd_explain(int family, const void* params, size_t params_bytes, int math_mode, const int64_t grid[3],
@@ -1155,20 +1205,35 @@ int pd_explain(int family, const void* params, size_t params_bytes, int math_mod
 }
 
 int pd_set_tuning(const char* key, int64_t value) {
-    if (!key) return PD_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(g_tuning_mutex);
-    auto it = tuning().find(key);
-    if (it == tuning().end()) return PD_ERR_INVALID_ARGUMENT;
-    it->second = value;
+    const int i = key ? knob_index(key) : -1;
+    if (i < 0) return PD_ERR_INVALID_ARGUMENT;
+    g_knobs[i].store(value, std::memory_order_relaxed);
     return PD_OK;
 }
 
 int pd_get_tuning(const char* key, int64_t* value) {
-    if (!key || !value) return PD_ERR_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(g_tuning_mutex);
-    auto it = tuning().find(key);
-    if (it == tuning().end()) return PD_ERR_INVALID_ARGUMENT;
-    *value = it->second;
+    const int i = key ? knob_index(key) : -1;
+    if (i < 0 || !value) return PD_ERR_INVALID_ARGUMENT;
+    *value = knob((Knob)i);
+    return PD_OK;
+}
+
+int pd_set_thread_tuning(const char* key, int64_t value) {
+    const int i = key ? knob_index(key) : -1;
+    if (i < 0) return PD_ERR_INVALID_ARGUMENT;
+    t_knobs.set[i] = true;
+    t_knobs.value[i] = value;
+    return PD_OK;
+}
+
+int pd_clear_thread_tuning(const char* key) {
+    if (!key) {
+        t_knobs = ThreadKnobs();
+        return PD_OK;
+    }
+    const int i = knob_index(key);
+    if (i < 0) return PD_ERR_INVALID_ARGUMENT;
+    t_knobs.set[i] = false;
     return PD_OK;
 }
 

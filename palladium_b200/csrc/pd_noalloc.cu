@@ -106,6 +106,13 @@ extern "C" int pd_gray_scott_static(const pd_gray_scott_params* p, int math_mode
                     "use pd_launch, which takes a workspace or allocates one",
                     (long long)rows_alloc, (long long)p->cols, PD_STATIC_GS_MAX_CELLS);
     if (!u || !v || !uo || !vo) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "gray_scott: NULL buffer");
+    // Grids narrower than 128 columns (or not a multiple of 4) run the one-thread-per-cell kernel, whose
+    // rows are spread over the second launch dimension, 8 per block, at most 65535 blocks.
+    if (!((p->cols % 4 == 0) && p->cols >= 128) && (rows_alloc + 7) / 8 > 65535)
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                    "gray_scott: %lld rows of %lld columns cannot be launched (grids narrower than 128 columns, or "
+                    "with a column count that is not a multiple of 4, take at most 524280 rows)",
+                    (long long)rows_alloc, (long long)p->cols);
     const size_t cells = (size_t)rows_alloc * (size_t)p->cols;
     const size_t field_bytes = cells * sizeof(float);
     cudaStream_t st = (cudaStream_t)cuda_stream;

@@ -62,7 +62,17 @@ static ffi::Error PalladiumCudaDispatch(int64_t family, ffi::Span<const uint8_t>
                                         int64_t grid_y, int64_t grid_z, int64_t threadgroup_x,
                                         int64_t threadgroup_y, int64_t threadgroup_z, int64_t math_mode,
                                         ffi::RemainingArgs args, ffi::RemainingRets rets) {
-  return Dispatch(family, params.begin(), params.size(), grid_x, grid_y, grid_z, threadgroup_x, threadgroup_y,
+  // The run-time compiled families hold host pointers (source text) in their parameter
+  // blocks; attribute bytes must never be read as such pointers.
+  if (family == PD_FAMILY_SOURCE || family == PD_FAMILY_CUSTOM_ODE)
+    return ffi::Error::InvalidArgument(
+        "palladium_cuda_dispatch: this family carries source text; call palladium_cuda_dispatch_source");
+  // An attribute span has no alignment guarantee, and the parameter blocks hold int64 / double fields.
+  alignas(8) unsigned char aligned_params[256];
+  if (params.size() > sizeof aligned_params)
+    return ffi::Error::InvalidArgument("palladium_cuda_dispatch: params block is larger than 256 bytes");
+  std::memcpy(aligned_params, params.begin(), params.size());
+  return Dispatch(family, aligned_params, params.size(), grid_x, grid_y, grid_z, threadgroup_x, threadgroup_y,
                   threadgroup_z, math_mode, args, rets);
 }
 

@@ -214,17 +214,18 @@ class BoundKernel:
             raise DispatchError(f"kernel takes {len(spec.inputs)} arrays, got {len(inputs)}")
         in_bytes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.inputs]
         out_bytes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.outputs]
-        for i, (t, b) in enumerate(zip(inputs, in_bytes)):
-            if not t.is_cuda or not t.is_contiguous():
-                raise DispatchError(f"argument {i}: expected a contiguous CUDA tensor")
-            if t.numel() * t.element_size() != b:
-                raise DispatchError(f"argument {i}: expected {b} bytes, got {t.numel() * t.element_size()}")
+        current = torch.cuda.current_device()
+        check_device_tensors("argument", inputs, in_bytes, current)
         st = stream if stream is not None else torch.cuda.current_stream()
         if outputs is None:
             with torch.cuda.stream(st):
                 outputs = [torch.empty(max(b, 1), dtype=torch.uint8, device="cuda") for b in out_bytes]
         elif len(outputs) != len(out_bytes):
             raise DispatchError(f"kernel produces {len(out_bytes)} arrays, got {len(outputs)} output tensors")
+        else:
+            # The kernel writes `out_bytes[i]` bytes from each pointer whatever the tensor's own
+            # size or strides: a short, strided, host or other-device tensor must stop here.
+            check_device_tensors("output", outputs, out_bytes, current)
         _native.launch(
             spec.family.family_id, spec.params, self.math_mode, spec.grid, self.threadgroup,
             [(t.data_ptr(), b) for t, b in zip(inputs, in_bytes)],
@@ -232,6 +233,24 @@ class BoundKernel:
             stream=st.cuda_stream,
         )
         return outputs
+
+
+def check_device_tensors(what: str, tensors, nbytes, device_index: int) -> None:
+    """Refuse, before any launch, a tensor the kernel could not safely read or
+    write: the native call is given a pointer and the byte count of the traced
+    operand, so the tensor must be on the launching CUDA device, contiguous, and
+    hold exactly that many bytes."""
+    for i, (t, b) in enumerate(zip(tensors, nbytes)):
+        if not getattr(t, "is_cuda", False):
+            raise DispatchError(f"{what} {i}: expected a CUDA tensor, got one on {getattr(t, 'device', 'the host')}")
+        if not t.is_contiguous():
+            raise DispatchError(f"{what} {i}: expected a contiguous tensor (a strided view cannot be passed by pointer)")
+        have = t.numel() * t.element_size()
+        if have != b:
+            raise DispatchError(f"{what} {i}: expected {b} bytes, got {have}")
+        index = getattr(t.device, "index", None)
+        if index is not None and index != device_index:
+            raise DispatchError(f"{what} {i}: tensor is on cuda:{index} but the launch runs on cuda:{device_index}")
 
 
 def bind(spec: KernelSpec, msl_source: str | None = None, *, math_mode=MathMode.FAST,

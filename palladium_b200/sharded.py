@@ -214,12 +214,26 @@ class GrayScottSlab:
         output sets alternate, so a neighbour never reads the set being written.
         CUDA step function only; the first call still fills the ghost rows with
         the point-to-point exchange.
+    timeout, block_host : how long a rank waits for its neighbours in an exchange
+        (seconds), and whether the host blocks in that wait.  With the host
+        blocking (the default for CPU fields) a neighbour that left the stepping
+        loop between calls ends the wait after `timeout` with a `DispatchError`
+        naming the ranks that never arrived, instead of waiting forever.  For
+        CUDA fields the default is a stream-ordered wait (the host runs ahead and
+        the launch queue stays full); there the process group's own timeout bounds
+        the wait, or pass `block_host=True` to get the bounded host wait.
     """
 
     def __init__(self, u, v, rows_total: int, *, halo: int = 4, constants: dict | None = None, math_mode="fast",
-                 group=None, step_fn: Callable | None = None, overlap: bool = False, push: bool = False):
+                 group=None, step_fn: Callable | None = None, overlap: bool = False, push: bool = False,
+                 timeout: float = 120.0, block_host: bool | None = None):
         import torch
 
+        if timeout <= 0:
+            raise ValueError("timeout must be positive (seconds)")
+        self.timeout = float(timeout)
+        self.block_host = (not u.is_cuda) if block_host is None else bool(block_host)
+        self.calls = 0
         self.overlap = overlap
         self.push = bool(push)
         if self.push and step_fn is not None:
@@ -341,7 +355,8 @@ class GrayScottSlab:
         if self.world > 1:
             # orders "every rank's call (and its stores into our ghost rows) has finished"
             # before anyone's next call reads them
-            _dist().all_reduce(self._flag, group=self.group)
+            self._wait([_dist().all_reduce(self._flag, group=self.group, async_op=True)],
+                       "the all-reduce that orders the calls of the in-kernel exchange")
         self._cur = out
         self.u, self.v = self._sets[out]
         self._ghosts_valid = True
@@ -397,8 +412,55 @@ class GrayScottSlab:
                     dist.P2POp(dist.isend, bot_send, self._global(self.down), group=self.group),
                     dist.P2POp(dist.irecv, f[:h], self._global(self.up), group=self.group),
                     dist.P2POp(dist.irecv, f[h + r:], self._global(self.down), group=self.group)]
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
+        self._wait(dist.batch_isend_irecv(ops), "the halo exchange")
+
+    def _wait(self, works, what: str) -> None:
+        """Wait for the collective(s) of one exchange.  Host-blocking waits are
+        bounded by `self.timeout`; when one runs out, the ranks that never
+        reached this exchange are looked up and named."""
+        self.calls += 1
+        if not self.block_host:
+            for work in works:
+                work.wait()
+            return
+        from datetime import timedelta
+
+        try:
+            for work in works:
+                work.wait(timedelta(seconds=self.timeout))
+        except RuntimeError as exc:      # a timeout, or a connection a departed peer closed
+            from .errors import DispatchError
+
+            raise DispatchError(self._missing_ranks_message(what, exc)) from exc
+
+    def _missing_ranks_message(self, what: str, exc: Exception) -> str:
+        """Every rank whose wait ran out posts its rank under this slab's key in the
+        job's key-value store; after a short grace period the ranks that posted
+        nothing are the ones that are gone (left the loop, raised, or died)."""
+        import time
+
+        waited_on = sorted({self._global(self.up), self._global(self.down)})
+        text = (f"rank {self.rank}: {what} with ranks {waited_on} did not complete within {self.timeout:g} s "
+                f"(exchange {self.calls} of this slab)")
+        try:
+            store = _dist().distributed_c10d._get_default_store()
+            me = self._global(self.rank)
+            store.set(f"palladium_b200/slab_wait/{me}", str(self.calls))
+            ranks = [self._global(r) for r in range(self.world)]
+            missing = ranks
+            deadline = time.monotonic() + min(2.0, self.timeout)
+            while True:
+                missing = [r for r in ranks if r != me and not store.check([f"palladium_b200/slab_wait/{r}"])]
+                if not missing or time.monotonic() > deadline:
+                    break
+                time.sleep(0.05)
+            if missing:
+                text += f"; rank(s) {missing} never arrived (left the stepping loop or stopped)"
+            else:
+                text += "; every rank is waiting in an exchange, so the ranks disagree on the number of calls"
+        except Exception:   # no store to ask: the neighbours waited on are all that is known
+            pass
+        return f"{text}: {exc}"
 
     def _exchange_pairwise(self) -> None:
         dist = _dist()
@@ -412,12 +474,10 @@ class GrayScottSlab:
             # message 1: my top rows -> the other's bottom ghosts; message 2: my bottom rows -> its top ghosts
             first = [dist.P2POp(dist.isend, top_send, other, group=self.group),
                      dist.P2POp(dist.irecv, bot_recv, other, group=self.group)]
-            for req in dist.batch_isend_irecv(first):
-                req.wait()
+            self._wait(dist.batch_isend_irecv(first), "the halo exchange")
             second = [dist.P2POp(dist.isend, bot_send, other, group=self.group),
                       dist.P2POp(dist.irecv, top_recv, other, group=self.group)]
-            for req in dist.batch_isend_irecv(second):
-                req.wait()
+            self._wait(dist.batch_isend_irecv(second), "the halo exchange")
 
     def _global(self, group_rank: int) -> int:
         dist = _dist()

@@ -89,6 +89,22 @@ def test_tuning_knobs_round_trip():
         _native.set_tuning("no_such_knob", 1)
 
 
+def test_thread_tuning_overrides_only_the_calling_thread():
+    import threading
+
+    seen = {}
+    with _native.thread_tuning(gs_variant=1, vdp_variant=0):
+        assert _native.get_tuning("gs_variant") == 1 and _native.get_tuning("vdp_variant") == 0
+        worker = threading.Thread(target=lambda: seen.update(other=_native.get_tuning("gs_variant")))
+        worker.start()
+        worker.join()
+    assert seen["other"] == -1                      # another thread kept the process-wide value
+    assert _native.get_tuning("gs_variant") == -1   # and the override ended with the block
+    with pytest.raises(KeyError):
+        with _native.thread_tuning(no_such_knob=1):
+            pass
+
+
 def test_launch_without_device_fails_loudly():
     if _native.device_count() > 0:
         pytest.skip("a GPU is present")

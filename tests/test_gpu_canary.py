@@ -98,13 +98,10 @@ def test_gray_scott_stays_in_bounds(shape, steps, halo, variant):
     full = (rows + 2 * halo, cols)
     u = (1 - 0.5 * rng.random(full)).astype(np.float32)
     v = (0.25 * rng.random(full)).astype(np.float32)
-    _native.set_tuning("gs_variant", variant)
-    try:
+    with _native.thread_tuning(gs_variant=variant):
         call = H.gs_solver(rows, cols, call=pd.cuda_call_jit, math_mode=pd.MathMode.SAFE, steps=steps, halo=halo)
         got = _run_guarded(call, [u, v])
         want = _plain(call, [u, v])
-    finally:
-        _native.set_tuning("gs_variant", -1)
     valid = slice(halo, full[0] - halo) if halo else slice(None)
     for g, w in zip(got, want):
         np.testing.assert_array_equal(g[valid], w[valid])

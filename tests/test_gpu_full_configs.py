@@ -63,12 +63,9 @@ def test_gray_scott_8192_fused_and_single_step_kernels_agree():
     steps = 18
     results = []
     for variant in (1, 2):
-        _native.set_tuning("gs_variant", variant)
-        try:
+        with _native.thread_tuning(gs_variant=variant):
             call = H.gs_solver(size, size, call=pd.cuda_call_jit, math_mode=SAFE, steps=steps)
             results.append(call(u, v))
-        finally:
-            _native.set_tuning("gs_variant", -1)
     assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
     # a window around a seeded patch corner equals the oracle run on the periodic sub-problem's light cone
     uo = results[1][0]

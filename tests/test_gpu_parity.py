@@ -75,18 +75,34 @@ def test_lv_rk4_items_per_thread_agree(items):
 
     n = 10_007
     args = W.lotka_volterra_ensemble(n)
-    _native.set_tuning("lv_items_per_thread", items)
-    try:
+    with _native.thread_tuning(lv_items_per_thread=items):
         got = H.lv_solver(n, steps=200, math_mode=SAFE)(*args)
-    finally:
-        _native.set_tuning("lv_items_per_thread", 0)
     want = oracle.lv_rk4(*args, dt=0.01, steps=200)
     np.testing.assert_array_equal(got[0], want[0])
     np.testing.assert_array_equal(got[1], want[1])
 
 
+def test_rk4_named_configuration_safe_is_bit_exact():
+    """The benchmark configuration itself -- N = 100 000, dt = 0.01, 1000 steps,
+    final state as one (N, 2) array -- under SAFE: every state equals the oracle's
+    bit for bit, which meets the stated rtol 1e-5 with zero difference."""
+    from palladium_b200 import families, pl
+
+    n = W.LV_CONFIG["n"]
+    args = W.lotka_volterra_ensemble(n, seed=W.LV_CONFIG["seed"])
+    stacked = pd.cuda_call(families.lv_rk4(W.LV_CONFIG["dt"], W.LV_CONFIG["steps"]), grid=(n,), in_specs=[H.SPEC_1] * 6,
+                           out_specs=pl.BlockSpec((1, 2), lambda i: (i, 0)),
+                           out_shape=pl.ShapeDtypeStruct((n, 2), np.float32), math_mode=SAFE)(*args)
+    want_x, want_y = oracle.lv_rk4(*args, dt=W.LV_CONFIG["dt"], steps=W.LV_CONFIG["steps"])
+    np.testing.assert_array_equal(stacked[:, 0], want_x)
+    np.testing.assert_array_equal(stacked[:, 1], want_y)
+    x, y = H.lv_solver(n, steps=W.LV_CONFIG["steps"], math_mode=SAFE)(*args)
+    np.testing.assert_array_equal(x, want_x)
+    np.testing.assert_array_equal(y, want_y)
+
+
 @pytest.mark.parametrize("mode", [RELAXED, FAST])
-def test_lv_rk4_config_relaxed_fast(mode):
+def test_rk4_named_configuration_fast_modes(mode):
     """The benchmark configuration: N = 100 000, dt = 0.01, 1000 steps.
 
     RELAXED contracts a*b+c into FMAs and FAST integrates the rescaled state
@@ -142,8 +158,13 @@ def test_lv_rk4_stacked_state_output(n):
         assert stacked.shape == (n, 2)
         np.testing.assert_array_equal(stacked[:, 0], x)
         np.testing.assert_array_equal(stacked[:, 1], y)
+    # and the stacked SAFE form equals the oracle
     want = oracle.lv_rk4(*ins, dt=0.01, steps=60)
-    np.testing.assert_array_equal(x if mode is SAFE else stacked[:, 0], stacked[:, 0])
+    safe = pd.cuda_call(families.lv_rk4(0.01, 60), grid=(n,), in_specs=[H.SPEC_1] * 6,
+                        out_specs=pl.BlockSpec((1, 2), lambda i: (i, 0)),
+                        out_shape=pl.ShapeDtypeStruct((n, 2), np.float32), math_mode=SAFE)(*ins)
+    np.testing.assert_array_equal(safe[:, 0], want[0])
+    np.testing.assert_array_equal(safe[:, 1], want[1])
 
 
 # ------------------------------------------------------------------ adaptive BS3(2)
@@ -158,11 +179,8 @@ def test_vdp_safe_counts_bit_exact(n, variant):
     from palladium_b200 import _native
 
     x0, v0, mu = W.van_der_pol_ensemble(n)
-    _native.set_tuning("vdp_variant", variant)
-    try:
+    with _native.thread_tuning(vdp_variant=variant):
         got = H.vdp_solver(n, outputs=6, math_mode=SAFE, **VDP_CFG)(x0, v0, mu)
-    finally:
-        _native.set_tuning("vdp_variant", 2)
     want = oracle.vdp_bs32(x0, v0, mu, pow="pd", **VDP_CFG)
     for g, w, name in zip(got, want, ("t", "x", "v", "steps", "rejected", "real")):
         np.testing.assert_array_equal(g, w, err_msg=name)
@@ -418,15 +436,10 @@ def test_gray_scott_temporal_blocking_bit_exact(shape, steps, fuse, persistent):
     rng = np.random.default_rng(8)
     u = (1.0 - 0.5 * rng.random(shape)).astype(np.float32)
     v = (0.25 * rng.random(shape)).astype(np.float32)
-    _native.set_tuning("gs_fuse", fuse)
-    _native.set_tuning("gs_persistent", persistent)
-    try:
+    with _native.thread_tuning(gs_fuse=fuse, gs_persistent=persistent):
         call = H.gs_solver(rows, cols, math_mode=SAFE, steps=steps)
         assert call.explain(u, v).cuda_kernel.startswith("pd_gs_tbp_kernel" if persistent else "pd_gs_tb_kernel")
         got_u, got_v = call(u, v)
-    finally:
-        _native.set_tuning("gs_fuse", 4)
-        _native.set_tuning("gs_persistent", 0)
     want_u, want_v = oracle.gray_scott(u, v, steps=steps)
     np.testing.assert_array_equal(got_u, want_u)
     np.testing.assert_array_equal(got_v, want_v)
@@ -437,11 +450,8 @@ def test_gray_scott_variants_agree(variant):
     from palladium_b200 import _native
 
     u, v = W.gray_scott_initial_state(256, seed=11, patches=8)
-    _native.set_tuning("gs_variant", variant)
-    try:
+    with _native.thread_tuning(gs_variant=variant):
         got_u, got_v = H.gs_solver(256, 256, math_mode=SAFE, steps=6)(u, v)
-    finally:
-        _native.set_tuning("gs_variant", -1)
     want_u, want_v = oracle.gray_scott(u, v, steps=6)
     np.testing.assert_array_equal(got_u, want_u)
     np.testing.assert_array_equal(got_v, want_v)

@@ -274,3 +274,38 @@ def test_public_names():
                  "KernelDiagnostics", "KernelSpec", "BlockInfo", "MathMode", "bind", "trace", "debug_msl",
                  "PalladiumError", "TraceError", "EmitError", "UnsupportedPrimitiveError", "DispatchError"):
         assert hasattr(pd, name), name
+
+
+def test_device_tensors_are_checked_before_any_launch():
+    """Outputs handed to the device path are validated like inputs: a host tensor, a
+    strided view, a short tensor or one on another GPU is refused before the native
+    call, which would write the traced byte count from the pointer regardless."""
+    import torch
+
+    from palladium_b200.dispatch import check_device_tensors
+
+    class OnGpu:   # what the check reads of a tensor, for shapes a CPU-only box cannot allocate on a device
+        is_cuda = True
+
+        def __init__(self, numel, contiguous=True, index=0):
+            self._numel, self._contiguous = numel, contiguous
+            self.device = torch.device("cuda", index)
+
+        def is_contiguous(self):
+            return self._contiguous
+
+        def numel(self):
+            return self._numel
+
+        def element_size(self):
+            return 4
+
+    check_device_tensors("output", [OnGpu(100)], [400], 0)
+    with pytest.raises(pd.DispatchError, match="output 0: expected a CUDA tensor"):
+        check_device_tensors("output", [torch.empty(100)], [400], 0)
+    with pytest.raises(pd.DispatchError, match="output 1: expected 400 bytes, got 396"):
+        check_device_tensors("output", [OnGpu(100), OnGpu(99)], [400, 400], 0)
+    with pytest.raises(pd.DispatchError, match="output 0: expected a contiguous tensor"):
+        check_device_tensors("output", [OnGpu(100, contiguous=False)], [400], 0)
+    with pytest.raises(pd.DispatchError, match="is on cuda:1 but the launch runs on cuda:0"):
+        check_device_tensors("output", [OnGpu(100, index=1)], [400], 0)

@@ -16,6 +16,7 @@ import oracle
 from oracle import oracle_np
 from palladium_b200 import sharded
 from palladium_b200 import workloads as W
+from palladium_b200.errors import DispatchError
 
 
 def test_partition_covers_everything_once():
@@ -72,6 +73,29 @@ def _worker(rank, world, port, case, out_dir):
             (lx, ly), _ = sharded.run_ensemble(make, ins, interleave=interleave)
             np.savez(os.path.join(out_dir, f"ens_{rank}.npz"), x=x, y=y, lx=lx, ly=ly,
                      idx=np.arange(n)[idx])
+        elif case == "leave":
+            # rank 2 returns from the stepping loop after its first exchange (between steps, nothing of
+            # its own in flight); the others find out through the bounded wait of their next exchange
+            rows, cols, halo = 48, 20, 3
+            u0, v0 = W.gray_scott_initial_state(rows, seed=11, patches=3, patch=8)
+            u0, v0 = u0[:, :cols].copy(), v0[:, :cols].copy()
+            lo, hi = sharded.partition(rows, world, rank)
+            slab = sharded.GrayScottSlab(torch.from_numpy(u0[lo:hi]), torch.from_numpy(v0[lo:hi]), rows, halo=halo,
+                                         constants=dict(oracle.GS_DEFAULTS), step_fn=_np_slab_step, timeout=1.5)
+            store = dist.distributed_c10d._get_default_store()
+            message = ""
+            if rank == 2:
+                slab.advance(halo)                       # one exchange, then it leaves
+                store.wait(["leave_case/0", "leave_case/1"])   # stays alive, on the host, until the others are done
+            else:
+                try:
+                    slab.advance(3 * halo)
+                except DispatchError as exc:
+                    message = str(exc)
+                store.set(f"leave_case/{rank}", "done")
+            with open(os.path.join(out_dir, f"leave_{rank}.txt"), "w") as fh:
+                fh.write(f"{slab.exchanges}\n{message}")
+            os._exit(0)    # the group is unusable after a collective that timed out: no orderly teardown
         elif case == "gbm":
             cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=32)
             res = sharded.gbm_monte_carlo(W.gbm_key(0), 1001, cfg, path_fn=_oracle_paths)
@@ -157,3 +181,17 @@ def test_gbm_all_reduce_matches_single_rank(tmp_path):
     # the slabs are contiguous and the per-path results do not depend on the rank count
     assert int(parts[0]["lo"]) == 0 and int(parts[0]["hi"]) == int(parts[1]["lo"]) and int(parts[1]["hi"]) == 1001
     np.testing.assert_array_equal(np.concatenate([p["out"] for p in parts]), single.local_output.numpy())
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_others_wait_with_its_name(tmp_path):
+    """World 3 on gloo: rank 2 returns after its first exchange.  The other two
+    ranks' next exchange runs into the bounded wait and raises DispatchError
+    naming rank 2, instead of waiting forever."""
+    _run(3, "leave", tmp_path)
+    gone = (tmp_path / "leave_2.txt").read_text().splitlines()
+    assert gone[0] == "1"
+    for rank in (0, 1):
+        exchanges, message = (tmp_path / f"leave_{rank}.txt").read_text().split("\n", 1)
+        assert int(exchanges) == 2                       # the first exchange completed, the second did not
+        assert "did not complete within 1.5 s" in message
+        assert "rank(s) [2] never arrived" in message

@@ -43,8 +43,12 @@ def _static(params, mode, u, v):
     return uo, vo
 
 
-@pytest.mark.parametrize("rows,cols,steps,halo", [(256, 256, 6, 0), (100, 60, 5, 0), (64, 512, 3, 4), (128, 128, 1, 0)])
+@pytest.mark.parametrize("rows,cols,steps,halo", [(256, 256, 6, 0), (100, 60, 5, 0), (64, 512, 3, 4), (128, 128, 1, 0),
+                                                  (64, 512, 4, 4), (50, 60, 2, 2)])
 def test_static_scratch_matches_regular_entry_point_twice(rows, cols, steps, halo):
+    """The even step counts with a halo are the cases where the last ping-pong lands
+    back in the caller's output after passing through the shared array while the
+    updated row window shrinks by one row per step on each side."""
     import torch
 
     mode = 0  # SAFE: identical kernels, identical op order -> identical bits
@@ -61,6 +65,36 @@ def test_static_scratch_matches_regular_entry_point_twice(rows, cols, steps, hal
         got_u, got_v = _static(params, mode, u, v)
         assert torch.equal(got_u[valid], want_u[valid])
         assert torch.equal(got_v[valid], want_v[valid])
+
+
+def test_static_scratch_matches_the_cpu_oracle():
+    """Not only equal to the regular entry point (the same kernels) but to the CPU
+    restatement of the reference's stencil, bit for bit under SAFE, on two calls in a row."""
+    import torch
+
+    import oracle
+
+    rows, cols, steps = 96, 260, 7
+    params = _native.GrayScottParams(0.16, 0.08, 0.035, 0.065, 1.0, steps, rows, cols, 0)
+    rng = np.random.default_rng(5)
+    for _ in range(2):
+        u0 = (1.0 - 0.5 * rng.random((rows, cols))).astype(np.float32)
+        v0 = (0.25 * rng.random((rows, cols))).astype(np.float32)
+        got_u, got_v = _static(params, 0, torch.from_numpy(u0).cuda(), torch.from_numpy(v0).cuda())
+        want_u, want_v = oracle.gray_scott(u0, v0, steps=steps)
+        np.testing.assert_array_equal(got_u.cpu().numpy(), want_u)
+        np.testing.assert_array_equal(got_v.cpu().numpy(), want_v)
+
+
+def test_static_scratch_rejects_a_grid_it_cannot_launch():
+    import torch
+
+    from palladium_b200.errors import DispatchError
+
+    params = _native.GrayScottParams(0.16, 0.08, 0.035, 0.065, 1.0, 2, 1 << 20, 1, 0)   # 2^20 cells, one column
+    buf = torch.zeros(16, device="cuda")
+    with pytest.raises(DispatchError, match="cannot be launched"):
+        _native.gray_scott_static(params, 0, buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), buf.data_ptr())
 
 
 def test_static_scratch_rejects_more_cells_than_it_holds():
