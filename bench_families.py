@@ -44,7 +44,7 @@ HBM_PEAK_FALLBACK_GBS = 6650.0
 def _hbm_peak_gbs() -> tuple[float, str]:
     from pathlib import Path
 
-    path = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+    path = Path(__file__).resolve().parent / "MEASURED_PEAKS.json"
     try:
         return float(json.loads(path.read_text())["hbm_gbs"]), "of measured (MEASURED_PEAKS.json hbm_gbs)"
     except Exception:

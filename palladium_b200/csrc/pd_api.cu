@@ -445,7 +445,12 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 launches = (p->steps + k - 1) / k;
             }
             plan->launches = launches;
-            plan->scratch_bytes = launches >= 2 ? 2 * rows_alloc * p->cols * (int64_t)sizeof(float) : 0;
+            // Intermediate fields.  A periodic grid ping-pongs between one scratch pair and the
+            // caller's output.  A slab never writes an intermediate state into its output: with
+            // the in-kernel exchange a neighbour may already have stored the next call's ghost
+            // rows there, so three or more launches alternate between two scratch pairs.
+            const int64_t pairs = launches < 2 ? 0 : (p->halo > 0 && launches >= 3 ? 2 : 1);
+            plan->scratch_bytes = pairs * 2 * rows_alloc * p->cols * (int64_t)sizeof(float);
             return PD_OK;
         }
         case PD_FAMILY_LV_RK4_DF32:
@@ -754,6 +759,10 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             float* ping_v = (float*)out[1];
             float* pong_u = (float*)scratch;
             float* pong_v = scratch ? (float*)((char*)scratch + field_bytes) : nullptr;
+            // slabs: a second scratch pair, so that only the final launch touches the output
+            const bool slab_pairs = p->halo > 0 && plan.launches >= 3;
+            float* pang_u = slab_pairs ? (float*)((char*)scratch + 2 * field_bytes) : nullptr;
+            float* pang_v = slab_pairs ? (float*)((char*)scratch + 3 * field_bytes) : nullptr;
             const float* src_u = (const float*)in[0];
             const float* src_v = (const float*)in[1];
             // Fused launches of k steps each (k = 1 for the one-step kernels); the
@@ -765,12 +774,18 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             while (done < p->steps) {
                 const int k = (int)((p->steps - done) < fuse ? (p->steps - done) : fuse);
                 a.u = src_u; a.v = src_v;
-                a.uo = to_out ? ping_u : pong_u;
-                a.vo = to_out ? ping_v : pong_v;
+                const bool last = done + k >= p->steps;
+                if (p->halo > 0) {
+                    // to_out alternates per launch; here it only picks between the scratch pairs
+                    a.uo = last ? ping_u : (slab_pairs && to_out ? pang_u : pong_u);
+                    a.vo = last ? ping_v : (slab_pairs && to_out ? pang_v : pong_v);
+                } else {
+                    a.uo = to_out ? ping_u : pong_u;
+                    a.vo = to_out ? ping_v : pong_v;
+                }
                 if (p->halo == 0) { a.row_lo = 0; a.row_hi = rows_alloc; }
                 else { a.row_lo = (int)(done + k); a.row_hi = rows_alloc - (int)(done + k); }
                 const int variant = k >= 2 ? tb_base + k : (plan.variant >= 12 ? 1 : plan.variant);
-                const bool last = done + k >= p->steps;
                 if (last && neighbours) {
                     // The final launch also feeds the neighbours' ghost rows: from its own
                     // stores when it is a temporally blocked launch, else by a copy kernel.

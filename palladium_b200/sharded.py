@@ -130,6 +130,9 @@ class GbmResult:
     sums: tuple[float, float]  # global (sum payoff, sum payoff^2)
 
 
+_GBM_CALLS: dict = {}
+
+
 def _cuda_gbm_paths(key, lo: int, n_local: int, constants: dict, math_mode, output: str):
     """Default path function: the CUDA kernel on this rank's GPU.  Returns
     (per-path output tensor, float64 tensor [sum payoff, sum payoff^2])."""
@@ -137,10 +140,16 @@ def _cuda_gbm_paths(key, lo: int, n_local: int, constants: dict, math_mode, outp
 
     from . import cuda_call_jit, families, pl
 
-    fam = families.gbm_threefry(output=output, path_offset=lo, **constants)
-    call = cuda_call_jit(fam, grid=(n_local,),
-                         out_shape=(pl.ShapeDtypeStruct((n_local,), np.float32), pl.ShapeDtypeStruct((2,), np.float64)),
-                         math_mode=math_mode)
+    cache_key = (lo, n_local, output, tuple(sorted(constants.items())), str(math_mode), torch.cuda.current_device())
+    call = _GBM_CALLS.get(cache_key)
+    if call is None:
+        fam = families.gbm_threefry(output=output, path_offset=lo, **constants)
+        call = cuda_call_jit(fam, grid=(n_local,),
+                             out_shape=(pl.ShapeDtypeStruct((n_local,), np.float32), pl.ShapeDtypeStruct((2,), np.float64)),
+                             math_mode=math_mode)
+        if len(_GBM_CALLS) >= 16:
+            _GBM_CALLS.clear()
+        _GBM_CALLS[cache_key] = call
     key_dev = torch.from_numpy(np.asarray(key, np.uint32).copy()).cuda()
     out, sums = call(key_dev)
     return out, sums
