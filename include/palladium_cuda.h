@@ -39,7 +39,7 @@ typedef enum pd_status {
     PD_ERR_INVALID_ARGUMENT = 1, /* maps to xla::ffi::Error::InvalidArgument (palladium_ffi.cpp:118-121) */
     PD_ERR_INTERNAL = 2,         /* maps to xla::ffi::Error::Internal (palladium_ffi.cpp:126,139,147,167) */
     PD_ERR_CUDA = 3,             /* a CUDA runtime call failed; message carries cudaGetErrorString */
-    PD_ERR_DEVICE_STATUS = 4     /* reserved for a kernel-reported status word; no kernel of this library waits on another, so none reports one */
+    PD_ERR_DEVICE_STATUS = 4     /* a kernel's bounded wait ran out (the register-tile stencil waits, with a limit, for its tile copies); see pd_device_status */
 } pd_status;
 
 /* MRMathMode ordinals as the reference passes them (src/palladium/ffi.py:38;
@@ -338,6 +338,18 @@ PD_API int pd_measure_int32_alu_peak(double* ops_per_s, char* err, size_t err_ca
  * stream), or a negative value if timing was not enabled.  Enable with
  * pd_set_tuning("time_kernels", 1); it adds an event pair and a synchronise. */
 PD_API double pd_last_kernel_ms(void);
+
+/* The status word of the current device: 0, or the code a kernel recorded when
+ * one of its bounded waits ran out (1: a tile copy of the register-tile stencil
+ * kernel did not arrive within its limit -- that call's outputs are not valid).
+ * No kernel of this library waits on another kernel or another GPU; the only
+ * device-side waits are a warp's waits for its own asynchronous tile copies.
+ * pd_dispatch_host checks the word itself after its final synchronise and
+ * returns PD_ERR_DEVICE_STATUS; after stream-ordered pd_launch calls, read it
+ * here once the stream has been synchronised.  `clear` != 0 resets it.
+ * No counterpart in the reference, whose dispatch blocks and reports through
+ * its status code alone (native/ffi/palladium_ffi.cpp:176-188). */
+PD_API int pd_device_status(int* code, int clear, char* err, size_t err_cap);
 
 /* Multi-step Gray-Scott on DEVICE buffers that allocates no device memory.
  * No counterpart in the reference (its stepping loop lets metal-runtime

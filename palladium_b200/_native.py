@@ -50,6 +50,7 @@ EXPORTED_SYMBOLS = (
     "pd_measure_fp32_fma_peak",
     "pd_measure_int32_alu_peak",
     "pd_last_kernel_ms",
+    "pd_device_status",
     "pd_gray_scott_static",
     "pd_custom_ode_check",
     "pd_source_kernel_check",
@@ -178,6 +179,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pd_measure_int32_alu_peak.argtypes = [ctypes.POINTER(_dbl), cp, sz]
     lib.pd_last_kernel_ms.restype = _dbl
     lib.pd_last_kernel_ms.argtypes = []
+    lib.pd_device_status.restype = ci
+    lib.pd_device_status.argtypes = [ctypes.POINTER(ci), ci, cp, sz]
     lib.pd_gray_scott_static.restype = ci
     lib.pd_gray_scott_static.argtypes = [ctypes.POINTER(GrayScottParams), ci, vp, vp, vp, vp, vp, cp, sz]
     lib.pd_gray_scott_slab_push.restype = ci
@@ -358,6 +361,17 @@ def measure_int32_alu_peak() -> float:
 
 def last_kernel_ms() -> float:
     return float(library().pd_last_kernel_ms())
+
+
+def device_status(clear: bool = True) -> int:
+    """pd_device_status: the code a kernel recorded on the current device when one of
+    its bounded waits ran out (0: none).  Read it after synchronising the stream."""
+    code = ctypes.c_int(0)
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_device_status(ctypes.byref(code), 1 if clear else 0, err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    return int(code.value)
 
 
 def gray_scott_static(params: GrayScottParams, math_mode: int, u: int, v: int, uo: int, vo: int,

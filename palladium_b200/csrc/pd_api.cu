@@ -62,7 +62,8 @@ int fail(int code, char* err, size_t cap, const char* fmt, ...) {
     X(gbm_blocks_per_sm, 0)                                                                                      \
     X(gs_variant, -1)          /* -1 = best for the shape; 0 per cell, 1 vec4 (one step), 2 temporal blocking */ \
     X(gs_fuse, 0)              /* steps fused per launch by variant 2; 0 = the kernel's default */              \
-    X(gs_persistent, 0)        /* variant 2: 0 one tile per block, 1 persistent blocks with cp.async prefetch, 2 TMA-fed */ \
+    X(gs_persistent, -1)       /* variant 2: 0 one tile per block, 1 persistent blocks + cp.async, 2 register tiles + TMA, -1 by size */ \
+    X(gs_wait_limit, 1 << 22)  /* register-tile kernel: polls of a tile copy's barrier before the warp gives up */ \
     X(df32_block, 128)                                                                                           \
     X(host_streams, 3)         /* streams the chunks of a host-buffer call rotate over (1..8) */                \
     X(host_chunks, -1)         /* chunks of a large host-buffer call (-1 = by size, 0 = ramped sizes) */        \
@@ -151,6 +152,54 @@ cudaError_t scratch_get(int device, void* stream, size_t bytes, void** out) {
     }
     *out = slot.ptr;
     return cudaSuccess;
+}
+
+// ---------------------------------------------------------------------------
+// Device status word.  Kernels whose waits are bounded (the register-tile
+// stencil waits for its tile copies) record a non-zero code here when a wait
+// runs out.  One word per device in pinned, device-mapped host memory: the
+// kernel writes it over the bus, the host reads it without a copy once the
+// stream has been synchronised.
+// ---------------------------------------------------------------------------
+const int kMaxStatusDevices = 64;
+std::mutex g_status_mutex;
+int* g_status_host[kMaxStatusDevices] = {};
+int* g_status_dev[kMaxStatusDevices] = {};
+cudaError_t status_word(int device, int** host, int** dev) {
+    if (device < 0 || device >= kMaxStatusDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    if (!g_status_host[device]) {
+        int* h = nullptr;
+        cudaError_t e = cudaHostAlloc((void**)&h, 64, cudaHostAllocMapped | cudaHostAllocPortable);
+        if (e != cudaSuccess) return e;
+        memset(h, 0, 64);
+        int* d = nullptr;
+        e = cudaHostGetDevicePointer((void**)&d, h, 0);
+        if (e != cudaSuccess) { cudaFreeHost(h); return e; }
+        g_status_host[device] = h;
+        g_status_dev[device] = d;
+    }
+    if (host) *host = g_status_host[device];
+    if (dev) *dev = g_status_dev[device];
+    return cudaSuccess;
+}
+
+// After a synchronise: a non-zero status word becomes PD_ERR_DEVICE_STATUS and is cleared.
+// A device that never ran a kernel with bounded waits has no word and nothing to report.
+int check_device_status(int device, char* err, size_t err_cap) {
+    if (device < 0 || device >= kMaxStatusDevices) return PD_OK;
+    volatile int* word;
+    {
+        std::lock_guard<std::mutex> lock(g_status_mutex);
+        word = g_status_host[device];
+    }
+    if (!word || *word == 0) return PD_OK;
+    const int code = *word;
+    *word = 0;
+    return fail(PD_ERR_DEVICE_STATUS, err, err_cap,
+                "device status %d: %s", code,
+                code == 1 ? "a tile copy of the stencil kernel did not arrive within its wait limit; the outputs of the call are not valid"
+                          : "a kernel reported a failed bounded wait");
 }
 
 thread_local double t_last_kernel_ms = -1.0;
@@ -432,16 +481,32 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                 plan->grid[1] = (rows_alloc + PD_GS_TILE_ROWS - 1) / PD_GS_TILE_ROWS;
             } else {
                 const int k = p->steps < fuse ? (int)p->steps : fuse;
-                const bool persistent = knob(K_gs_persistent) != 0;
-                plan->variant = (persistent ? 20 : 10) + k;  // the kernel of the full-size launches
+                // 0: one tile per block in shared memory; 1: persistent blocks with cp.async prefetch;
+                // 2: one tile per warp in registers, tiles fetched by the copy engine (TMA).
+                // -1: the register-tile kernel once there are tiles for every resident warp, since
+                // a warp works through its tile alone (small grids finish sooner spread over blocks).
+                int form = (int)knob(K_gs_persistent);
+                const int64_t tiles = ((p->cols + 119) / 120) * ((rows_alloc + PD_GS_RT_ROWS - 1) / PD_GS_RT_ROWS);
+                if (form < 0) form = tiles >= (int64_t)dev.sms * 8 ? 2 : 0;
+                if (form > 2) form = 2;
+                plan->variant = (form == 2 ? 30 : form == 1 ? 20 : 10) + k;  // the kernel of the full-size launches
                 plan->kernel = mt->kernel_ptr(family, plan->variant);
-                plan->kernel_name = persistent
-                    ? (k == 4 ? "pd_gs_tbp_kernel<4>" : k == 3 ? "pd_gs_tbp_kernel<3>" : "pd_gs_tbp_kernel<2>")
-                    : (k == 4 ? "pd_gs_tb_kernel<4>" : k == 3 ? "pd_gs_tb_kernel<3>" : "pd_gs_tb_kernel<2>");
+                static const char* const names[3][3] = {
+                    {"pd_gs_tb_kernel<2>", "pd_gs_tb_kernel<3>", "pd_gs_tb_kernel<4>"},
+                    {"pd_gs_tbp_kernel<2>", "pd_gs_tbp_kernel<3>", "pd_gs_tbp_kernel<4>"},
+                    {"pd_gs_rt_kernel<2>", "pd_gs_rt_kernel<3>", "pd_gs_rt_kernel<4>"}};
+                plan->kernel_name = names[form][k - 2];
                 plan->items = 4;  // cells per thread per row
-                plan->block[0] = 256;
-                plan->grid[0] = (p->cols + 119) / 120;
-                plan->grid[1] = (rows_alloc + PD_GS_TB_ROWS - 1) / PD_GS_TB_ROWS;
+                if (form == 2) {
+                    plan->block[0] = PD_GS_RT_WARPS * 32;
+                    int64_t g = (int64_t)dev.sms * PD_GS_RT_BLOCKS;
+                    if (g > (tiles + PD_GS_RT_WARPS - 1) / PD_GS_RT_WARPS) g = (tiles + PD_GS_RT_WARPS - 1) / PD_GS_RT_WARPS;
+                    plan->grid[0] = g > 0 ? g : 1;
+                } else {
+                    plan->block[0] = 256;
+                    plan->grid[0] = (p->cols + 119) / 120;
+                    plan->grid[1] = (rows_alloc + PD_GS_TB_ROWS - 1) / PD_GS_TB_ROWS;
+                }
                 launches = (p->steps + k - 1) / k;
             }
             plan->launches = launches;
@@ -767,8 +832,17 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             const float* src_v = (const float*)in[1];
             // Fused launches of k steps each (k = 1 for the one-step kernels); the
             // last launch must land in `out`, so an odd launch count starts there.
-            const int tb_base = plan.variant >= 22 ? 20 : 10;
+            const int tb_base = plan.variant >= 32 ? 30 : (plan.variant >= 22 ? 20 : 10);
             const int fuse = plan.variant >= 12 ? plan.variant - tb_base : 1;
+            if (tb_base == 30) {
+                // bounded waits of the tile copies: about a second of polling before a warp gives up
+                // (a copy takes microseconds), then a longer bound for the copy in flight to land
+                int* status_dev = nullptr;
+                PD_CUDA_TRY(status_word(dev.device, nullptr, &status_dev));
+                a.status = status_dev;
+                a.wait_limit = knob(K_gs_wait_limit);
+                a.drain_limit = (long long)1 << 24;
+            }
             bool to_out = (plan.launches % 2) == 1;
             int64_t done = 0;
             while (done < p->steps) {
@@ -898,6 +972,33 @@ struct HostStaging {
 thread_local HostStaging t_staging;
 
 }  // namespace
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point table (no link against libcuda).
+cudaError_t pd_encode_field_map(CUtensorMap* map, const float* base, int rows, int cols, int box_rows) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status) == cudaSuccess &&
+            status == cudaDriverEntryPointSuccess)
+            encode = reinterpret_cast<EncodeFn>(fn);
+        else
+            cudaGetLastError();
+    });
+    if (!encode) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};   // bytes between rows; a multiple of 16
+    const cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1u, 1u};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
 
 extern "C" {
 
@@ -1158,6 +1259,7 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
             if (e != cudaSuccess && rc == PD_OK)
                 rc = fail(PD_ERR_CUDA, err, err_cap, "cudaStreamSynchronize failed: %s", cudaGetErrorString(e));
         }
+        if (rc == PD_OK) rc = check_device_status(dev.device, err, err_cap);
         return rc;
     }
 
@@ -1180,6 +1282,7 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
     cudaError_t e = cudaStreamSynchronize(hs.stream);
     if (e != cudaSuccess && rc == PD_OK)
         rc = fail(PD_ERR_CUDA, err, err_cap, "cudaStreamSynchronize failed: %s", cudaGetErrorString(e));
+    if (rc == PD_OK) rc = check_device_status(dev.device, err, err_cap);
     return rc;
 }
 
@@ -1291,5 +1394,19 @@ int pd_measure_int32_alu_peak(double* ops_per_s, char* err, size_t err_cap) {
 }
 
 double pd_last_kernel_ms(void) { return t_last_kernel_ms; }
+
+int pd_device_status(int* code, int clear, char* err, size_t err_cap) {
+    if (!code) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "code must not be NULL");
+    DeviceFacts dev = device_facts();
+    if (!dev.present) return fail(PD_ERR_CUDA, err, err_cap, "no CUDA device is available");
+    volatile int* word = nullptr;
+    if (dev.device >= 0 && dev.device < kMaxStatusDevices) {
+        std::lock_guard<std::mutex> lock(g_status_mutex);
+        word = g_status_host[dev.device];
+    }
+    *code = word ? *word : 0;   // no word yet: no kernel with bounded waits has run on this device
+    if (word && clear) *word = 0;
+    return PD_OK;
+}
 
 }  // extern "C"

@@ -7,6 +7,7 @@
 #ifndef PD_KERNELS_H_
 #define PD_KERNELS_H_
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -76,6 +77,11 @@ struct PdGsArgs {
     int top_lo, top_hi, up_shift;
     int bot_lo, bot_hi, dn_shift;
     float *up_u, *up_v, *dn_u, *dn_v;
+    // Register-tile kernel: bound on the polls of a tile copy's barrier, the longer bound used once
+    // the first has run out (the copy in flight must land before the block may exit), and the word
+    // that receives a non-zero code when a wait ran out (device-visible, may be null).
+    long long wait_limit, drain_limit;
+    int* status;
 };
 
 struct PdDfLvArgs {
@@ -131,5 +137,17 @@ cudaError_t pd_launch_int_chain(uint32_t* sink, int iters, int grid, int block, 
 static const int PD_GS_TILE_ROWS = 32;
 static const int PD_GS_BLOCK = 128;
 #define PD_GS_TB_ROWS 16  /* output rows per block of the temporally blocked kernel */
+#ifndef PD_GS_RT_ROWS
+#define PD_GS_RT_ROWS 16  /* output rows per warp of the register-tile kernel */
+#define PD_GS_RT_WARPS 4  /* warps per block */
+#define PD_GS_RT_BLOCKS 2 /* blocks per SM the register budget allows */
+#endif
+#ifndef PD_GS_RT_GROUP
+#define PD_GS_RT_GROUP 2  /* tile rows advanced per straight-line block (1 or 2; tile heights are even) */
+#endif
+
+// A 2-D tensor map over one row-major float32 field of this GPU (rows x cols), box = box_rows x 128
+// columns, out-of-range elements read as zero.  Implemented once, in the C-ABI translation unit.
+cudaError_t pd_encode_field_map(CUtensorMap* map, const float* base, int rows, int cols, int box_rows);
 
 #endif  // PD_KERNELS_H_

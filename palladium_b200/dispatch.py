@@ -25,7 +25,7 @@ from pathlib import Path
 import numpy as np
 
 from . import _native
-from .errors import DispatchError
+from .errors import DispatchError, PalladiumError
 from .families import KernelSpec
 from .math_mode import MathMode, math_mode_ordinal
 
@@ -83,6 +83,13 @@ class PendingResult:
 
     def wait(self):
         self.event.synchronize()
+        # A kernel whose bounded wait ran out recorded a code instead of computing: report it
+        # rather than return fields that were never written (the eager call is blocking, like
+        # mr_dispatch in the reference, so this is where its status surfaces).
+        code = _native.device_status()
+        if code:
+            raise PalladiumError(f"device status {code}: a kernel's bounded wait ran out (a tile copy did not arrive "
+                                 "within its limit); the outputs of this call are not valid")
         outs = tuple(
             host.numpy().view(info.dtype).reshape(info.array_shape) for host, info in zip(self.out_host, self.out_infos)
         )

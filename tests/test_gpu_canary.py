@@ -91,14 +91,17 @@ def test_gbm_stays_in_bounds(n):
 
 @pytest.mark.parametrize("shape,steps,halo", [((7, 9), 3, 0), ((33, 132), 5, 0), ((17, 128), 4, 0), ((40, 244), 9, 0),
                                               ((48, 256), 4, 4), ((20, 128), 2, 3)])
-@pytest.mark.parametrize("variant", [-1, 1])
+@pytest.mark.parametrize("variant", [-1, 1, "register tiles"])
 def test_gray_scott_stays_in_bounds(shape, steps, halo, variant):
     rows, cols = shape
+    form = -1
+    if variant == "register tiles":   # the copy-engine fed kernel, forced also on grids the planner gives to the block kernel
+        variant, form = -1, 2
     rng = np.random.default_rng(3)
     full = (rows + 2 * halo, cols)
     u = (1 - 0.5 * rng.random(full)).astype(np.float32)
     v = (0.25 * rng.random(full)).astype(np.float32)
-    with _native.thread_tuning(gs_variant=variant):
+    with _native.thread_tuning(gs_variant=variant, gs_persistent=form):
         call = H.gs_solver(rows, cols, call=pd.cuda_call_jit, math_mode=pd.MathMode.SAFE, steps=steps, halo=halo)
         got = _run_guarded(call, [u, v])
         want = _plain(call, [u, v])

@@ -423,7 +423,7 @@ def test_gray_scott_safe_bit_exact(shape, steps):
     np.testing.assert_array_equal(got_v, want_v)
 
 
-@pytest.mark.parametrize("persistent", [0, 1])
+@pytest.mark.parametrize("persistent", [0, 1, 2])
 @pytest.mark.parametrize("fuse", [2, 3, 4])
 @pytest.mark.parametrize("shape,steps", [((256, 1024), 9), ((96, 256), 4), ((33, 132), 5), ((40, 128), 7),
                                          ((64, 360), 8), ((31, 244), 3), ((5, 128), 6)])
@@ -438,7 +438,7 @@ def test_gray_scott_temporal_blocking_bit_exact(shape, steps, fuse, persistent):
     v = (0.25 * rng.random(shape)).astype(np.float32)
     with _native.thread_tuning(gs_fuse=fuse, gs_persistent=persistent):
         call = H.gs_solver(rows, cols, math_mode=SAFE, steps=steps)
-        assert call.explain(u, v).cuda_kernel.startswith("pd_gs_tbp_kernel" if persistent else "pd_gs_tb_kernel")
+        assert call.explain(u, v).cuda_kernel.startswith(("pd_gs_tb_kernel", "pd_gs_tbp_kernel", "pd_gs_rt_kernel")[persistent])
         got_u, got_v = call(u, v)
     want_u, want_v = oracle.gray_scott(u, v, steps=steps)
     np.testing.assert_array_equal(got_u, want_u)
@@ -453,6 +453,51 @@ def test_gray_scott_variants_agree(variant):
     with _native.thread_tuning(gs_variant=variant):
         got_u, got_v = H.gs_solver(256, 256, math_mode=SAFE, steps=6)(u, v)
     want_u, want_v = oracle.gray_scott(u, v, steps=6)
+    np.testing.assert_array_equal(got_u, want_u)
+    np.testing.assert_array_equal(got_v, want_v)
+
+
+@pytest.mark.parametrize("shape,steps", [((256, 1024), 8), ((512, 2048), 12), ((100, 1000), 7), ((48, 16384), 6)])
+def test_gray_scott_register_tiles_fetched_by_the_copy_engine(shape, steps):
+    """The register-tile kernel on grids with interior tiles (fetched by bulk tensor
+    copies) as well as seam tiles (fetched with wrapped ordinary loads), several tiles
+    per warp so that the prefetch chain and the barrier's phase are exercised; the
+    widest case has the column count of the 8-GPU configuration."""
+    from palladium_b200 import _native
+
+    rows, cols = shape
+    rng = np.random.default_rng(12)
+    u = (1.0 - 0.5 * rng.random(shape)).astype(np.float32)
+    v = (0.25 * rng.random(shape)).astype(np.float32)
+    with _native.thread_tuning(gs_persistent=2):
+        call = H.gs_solver(rows, cols, math_mode=SAFE, steps=steps)
+        assert call.explain(u, v).cuda_kernel.startswith("pd_gs_rt_kernel")
+        got_u, got_v = call(u, v)
+    want_u, want_v = oracle.gray_scott(u, v, steps=steps)
+    np.testing.assert_array_equal(got_u, want_u)
+    np.testing.assert_array_equal(got_v, want_v)
+    assert _native.device_status() == 0
+
+
+def test_gray_scott_register_tiles_bounded_wait_reports_a_status():
+    """A correct launch whose wait limit is zero polls: every warp gives up on its
+    first tile copy at once, records the status code, still waits (bounded) for the
+    copy in flight to land, and returns; the host call reports the status instead
+    of handing back fields that were never computed, and the context stays usable."""
+    from palladium_b200 import _native
+
+    rows, cols = 256, 1024
+    rng = np.random.default_rng(13)
+    u = (1.0 - 0.5 * rng.random((rows, cols))).astype(np.float32)
+    v = (0.25 * rng.random((rows, cols))).astype(np.float32)
+    with _native.thread_tuning(gs_persistent=2, gs_wait_limit=0):
+        call = H.gs_solver(rows, cols, math_mode=SAFE, steps=4)
+        with pytest.raises(pd.PalladiumError, match="device status 1"):
+            call(u, v)
+    assert _native.device_status() == 0          # reported once, then cleared
+    with _native.thread_tuning(gs_persistent=2):
+        got_u, got_v = H.gs_solver(rows, cols, math_mode=SAFE, steps=4)(u, v)
+    want_u, want_v = oracle.gray_scott(u, v, steps=4)
     np.testing.assert_array_equal(got_u, want_u)
     np.testing.assert_array_equal(got_v, want_v)
 

@@ -28,13 +28,15 @@ def _state(rows, cols, seed=11):
     (40, 100, 4, 12),     # columns not a multiple of 4: per-cell kernel + copy kernel
     (16, 512, 16, 32),    # the slab is exactly one halo deep: top and bottom rows are the same rows
 ])
-def test_single_slab_wrapping_onto_itself(rows, cols, halo, steps):
+@pytest.mark.parametrize("form", [0, 2])   # tiles in shared memory per block / in registers per warp (copy-engine fed)
+def test_single_slab_wrapping_onto_itself(rows, cols, halo, steps, form):
     import torch
 
     u0, v0 = _state(rows, cols)
     slab = sharded.GrayScottSlab(torch.from_numpy(u0).cuda(), torch.from_numpy(v0).cuda(), rows, halo=halo,
                                  constants=dict(oracle.GS_DEFAULTS), math_mode="safe", push=True)
-    slab.advance(steps)
+    with _native.thread_tuning(gs_persistent=form):
+        slab.advance(steps)
     want_u, want_v = oracle.gray_scott(u0, v0, steps=steps)
     u, v = slab.owned()
     np.testing.assert_array_equal(u.cpu().numpy(), want_u)
@@ -43,8 +45,9 @@ def test_single_slab_wrapping_onto_itself(rows, cols, halo, steps):
     slab.close()
 
 
+@pytest.mark.parametrize("form", [0, 2])
 @pytest.mark.parametrize("halo,cycles", [(8, 3), (16, 2), (12, 3)])
-def test_two_slabs_of_unequal_height_pushing_into_each_other(halo, cycles):
+def test_two_slabs_of_unequal_height_pushing_into_each_other(halo, cycles, form):
     """Two 'ranks' in one process: A owns rows [0, 48), B owns [48, 128).  Each call
     pushes into the other's output set; the calls run back to back on one stream,
     so A's whole call -- its push into B's ghost rows included -- is over before
@@ -75,22 +78,24 @@ def test_two_slabs_of_unequal_height_pushing_into_each_other(halo, cycles):
         b[0][f][:halo] = a[0][f][rows_a:rows_a + halo]
         b[0][f][halo + rows_b:] = a[0][f][halo:2 * halo]
     cur = 0
-    for _ in range(cycles):
-        out = 1 - cur
-        for me, other, rows, other_rows in ((a, b, rows_a, rows_b), (b, a, rows_b, rows_a)):
-            params = _native.GrayScottParams(g["du"], g["dv"], g["f"], g["k"], g["dt"], halo, rows, cols, halo)
-            nb = _native.GsNeighbours(other[out][0].data_ptr(), other[out][1].data_ptr(), other_rows,
-                                      other[out][0].data_ptr(), other[out][1].data_ptr(), other_rows)
-            _native.gray_scott_slab_push(params, mode, me[cur][0].data_ptr(), me[cur][1].data_ptr(),
-                                         me[out][0].data_ptr(), me[out][1].data_ptr(), nb,
-                                         torch.cuda.current_stream().cuda_stream)
-        cur = out
+    with _native.thread_tuning(gs_persistent=form):
+        for _ in range(cycles):
+            out = 1 - cur
+            for me, other, rows, other_rows in ((a, b, rows_a, rows_b), (b, a, rows_b, rows_a)):
+                params = _native.GrayScottParams(g["du"], g["dv"], g["f"], g["k"], g["dt"], halo, rows, cols, halo)
+                nb = _native.GsNeighbours(other[out][0].data_ptr(), other[out][1].data_ptr(), other_rows,
+                                          other[out][0].data_ptr(), other[out][1].data_ptr(), other_rows)
+                _native.gray_scott_slab_push(params, mode, me[cur][0].data_ptr(), me[cur][1].data_ptr(),
+                                             me[out][0].data_ptr(), me[out][1].data_ptr(), nb,
+                                             torch.cuda.current_stream().cuda_stream)
+            cur = out
     torch.cuda.synchronize()
     want_u, want_v = oracle.gray_scott(u0, v0, steps=cycles * halo)
     got_u = torch.cat([a[cur][0][halo:halo + rows_a], b[cur][0][halo:halo + rows_b]]).cpu().numpy()
     got_v = torch.cat([a[cur][1][halo:halo + rows_a], b[cur][1][halo:halo + rows_b]]).cpu().numpy()
     np.testing.assert_array_equal(got_u, want_u)
     np.testing.assert_array_equal(got_v, want_v)
+    assert _native.device_status() == 0
 
 
 def test_argument_checks():
