@@ -813,8 +813,7 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             PdGsArgs a = {};
             a.rows_alloc = rows_alloc; a.cols = (int)p->cols;
             a.periodic_rows = p->halo == 0 ? 1 : 0;
-            a.du = (float)p->du; a.dv = (float)p->dv; a.f = (float)p->f; a.fk = (float)(p->f + p->k);
-            a.dt = (float)p->dt;
+            pd_gs_set_constants(a, p->du, p->dv, p->f, p->k, p->dt);
             if (p->steps == 0) {
                 PD_CUDA_TRY(cudaMemcpyAsync(out[0], in[0], field_bytes, cudaMemcpyDeviceToDevice, st));
                 PD_CUDA_TRY(cudaMemcpyAsync(out[1], in[1], field_bytes, cudaMemcpyDeviceToDevice, st));

@@ -146,6 +146,11 @@ static const int PD_GS_BLOCK = 128;
 #define PD_GS_RT_GROUP 2  /* tile rows advanced per straight-line block (1 or 2; tile heights are even) */
 #endif
 
+// The stencil's constants from the call's parameters (double on the host, rounded once each).
+inline void pd_gs_set_constants(PdGsArgs& a, double du, double dv, double f, double k, double dt) {
+    a.du = (float)du; a.dv = (float)dv; a.f = (float)f; a.fk = (float)(f + k); a.dt = (float)dt;
+}
+
 // A 2-D tensor map over one row-major float32 field of this GPU (rows x cols), box = box_rows x 128
 // columns, out-of-range elements read as zero.  Implemented once, in the C-ABI translation unit.
 cudaError_t pd_encode_field_map(CUtensorMap* map, const float* base, int rows, int cols, int box_rows);

@@ -132,7 +132,7 @@ extern "C" int pd_gray_scott_static(const pd_gray_scott_params* p, int math_mode
     a.rows_alloc = (int)rows_alloc;
     a.cols = (int)p->cols;
     a.periodic_rows = p->halo == 0 ? 1 : 0;
-    a.du = (float)p->du; a.dv = (float)p->dv; a.f = (float)p->f; a.fk = (float)(p->f + p->k); a.dt = (float)p->dt;
+    pd_gs_set_constants(a, p->du, p->dv, p->f, p->k, p->dt);
     const bool vec = (p->cols % 4 == 0) && p->cols >= 128 && aligned16(u) && aligned16(v) && aligned16(uo) && aligned16(vo);
     const int variant = vec ? 1 : 0;
 
