@@ -34,8 +34,11 @@ DF_SQRT = 1 + 3 + DF_ADD + 1 + 1 + 3
 # LV: 4 rhs x (5 mul + 2 sub) + 3 advances x 2 x (mul + add) + combine 2 x (2 mul + 3 add) + final advance 2 x (mul + add)
 DF32_LV_FLOPS = 4 * (5 * DF_MUL + 2 * DF_ADD) + 3 * 2 * (DF_MUL + DF_ADD) + 2 * (2 * DF_MUL + 3 * DF_ADD) + 2 * (DF_MUL + DF_ADD)
 DF_RECIP = 1 + 3 + 2 + 2 + 1 + 3
-# Kepler rhs: 2 mul + add, sqrt, mul, reciprocal, mul by GM, 2 mul  (negation is free)
-_KEP_RHS = 2 * DF_MUL + DF_ADD + DF_SQRT + DF_MUL + DF_RECIP + DF_MUL + 2 * DF_MUL
+# reciprocal square root: a/2, three float Newton steps of 4, two_prod, df_mul, residual 2, second-order term 3,
+# correction 2, fast_two_sum 3 (the integer seed is not a float operation)
+DF_RSQRT = 1 + 3 * 4 + 3 + DF_MUL + 2 + 3 + 2 + 3
+# Kepler rhs: 2 mul + add, reciprocal square root, its cube (2 mul), 2 mul; GM = 1 costs nothing (negation is free)
+_KEP_RHS = 2 * DF_MUL + DF_ADD + DF_RSQRT + 2 * DF_MUL + 2 * DF_MUL
 # combine: two exact doublings (2 flops each) and three adds per component
 DF32_KEPLER_FLOPS = 4 * _KEP_RHS + 3 * 4 * (DF_MUL + DF_ADD) + 4 * (2 * 2 + 3 * DF_ADD) + 4 * (DF_MUL + DF_ADD)
 HBM_PEAK_FALLBACK_GBS = 6650.0

@@ -344,7 +344,7 @@ def gray_scott(u, v, *, steps: int, **params):
 
 # --------------------------------------------------------------------------- df32
 def df_op(op: str, a_hi, a_lo, b_hi=None, b_lo=None):
-    code = {"add": 0, "sub": 1, "mul": 2, "div": 3, "sqrt": 4, "recip": 5}[op]
+    code = {"add": 0, "sub": 1, "mul": 2, "div": 3, "sqrt": 4, "recip": 5, "rsqrt": 6}[op]
     a_hi, a_lo = _f32(a_hi), _f32(a_lo)
     b_hi = _f32(b_hi) if b_hi is not None else np.ones_like(a_hi)
     b_lo = _f32(b_lo) if b_lo is not None else np.zeros_like(a_hi)

@@ -67,5 +67,24 @@ static inline df df_sqrt(df a) {
     df d = df_sub(a, two_prod(s, s));
     return quick_two_sum(s, d.hi / (s + s));
 }
+/* 1 / sqrt(a), a > 0: integer seed, three float Newton steps, one second-order correction in df32 */
+static inline df df_rsqrt(df a) {
+    union { float f; unsigned u; } bits;
+    float half_a = 0.5f * a.hi, y, e;
+    df t;
+    int i;
+    bits.f = a.hi;
+    bits.u = 0x5F375A86u - (bits.u >> 1);
+    y = bits.f;
+    for (i = 0; i < 3; ++i) {
+        float yy = y * y;
+        float h = half_a * yy;
+        y = y * (1.5f - h);
+    }
+    t = df_mul(a, two_prod(y, y));
+    e = (1.0f - t.hi) - t.lo;
+    e = fmaf(0.75f * e, e, e);                       /* second-order term of (1 - e)^(-1/2) */
+    return quick_two_sum(y, (0.5f * y) * e);
+}
 
 #endif  /* ORACLE_DF32_OPS_H_ */

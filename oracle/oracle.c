@@ -338,7 +338,7 @@ ORC_API int orc_gray_scott(int64_t rows, int64_t cols, const float* u, const flo
 /* ------------------------------------------------------------------------- */
 #include "df32_ops.h"
 
-/* elementwise df32 primitives, for exactness tests: op 0 add, 1 sub, 2 mul, 3 div, 4 sqrt(a) */
+/* elementwise df32 primitives, for exactness tests: op 0 add, 1 sub, 2 mul, 3 div, 4 sqrt(a), 5 1/a, 6 1/sqrt(a) */
 ORC_API void orc_df_op(int op, int64_t n, const float* ah, const float* al, const float* bh, const float* bl,
                        float* oh, float* ol) {
     for (int64_t i = 0; i < n; ++i) {
@@ -349,6 +349,7 @@ ORC_API void orc_df_op(int op, int64_t n, const float* ah, const float* al, cons
             case 2: r = df_mul(a, b); break;
             case 3: r = df_div(a, b); break;
             case 5: r = df_recip(a); break;
+            case 6: r = df_rsqrt(a); break;
             default: r = df_sqrt(a); break;
         }
         oh[i] = r.hi; ol[i] = r.lo;
@@ -409,9 +410,9 @@ ORC_API void orc_kepler_rk4_df32(int64_t n, const float* const* in, float* const
             for (int c = 0; c < 4; ++c) w[c] = s[c];
             for (int st = 0; st < 4; ++st) {
                 df r2 = df_add(df_mul(w[0], w[0]), df_mul(w[1], w[1]));
-                df r = df_sqrt(r2);
-                df r3 = df_mul(r2, r);
-                df g = df_mul(gm, df_recip(r3));
+                df rs = df_rsqrt(r2);                    /* 1 / |r| */
+                df g = df_mul(df_mul(rs, rs), rs);       /* 1 / |r|^3 */
+                if (!(gm.hi == 1.0f && gm.lo == 0.0f)) g = df_mul(gm, g);
                 k[st][0] = w[2];
                 k[st][1] = w[3];
                 k[st][2] = df_neg(df_mul(w[0], g));

@@ -239,6 +239,25 @@ PD_HD pd_df32 pd_df_sqrt(pd_df32 a) {
     return pd_fast_two_sum(s, corr);
 }
 
+// 1 / sqrt(a) for a > 0.  The seed is the integer estimate 0x5F375A86 - (bits >> 1)
+// (within 3.5 %), refined by three float Newton steps y <- y (3/2 - (a/2) y^2) to
+// float accuracy; every operation is a plain IEEE one, so host and device agree bit
+// for bit (the hardware's approximate rsqrt would be shorter but is not reproducible
+// off the GPU).  The last correction is carried out in df32 and to second order,
+// rs = y (1 + e/2 + 3 e^2/8) with e = 1 - a y^2 formed from error-free products
+// (e ~ 2^-22, so what is left is O(e^3), far below the pair's 2^-48).
+PD_HD pd_df32 pd_df_rsqrt(pd_df32 a) {
+    const float half_a = pd_mul(0.5f, a.hi);
+    float y = pd_u2f(0x5F375A86u - (pd_f2u(a.hi) >> 1));
+    y = pd_mul(y, pd_sub(1.5f, pd_mul(half_a, pd_mul(y, y))));
+    y = pd_mul(y, pd_sub(1.5f, pd_mul(half_a, pd_mul(y, y))));
+    y = pd_mul(y, pd_sub(1.5f, pd_mul(half_a, pd_mul(y, y))));
+    const pd_df32 t = pd_df_mul(a, pd_two_prod(y, y));           // a y^2 = 1 + O(2^-22)
+    float e = pd_sub(pd_sub(1.0f, t.hi), t.lo);                  // 1 - t.hi is exact (Sterbenz)
+    e = pd_fma(pd_mul(0.75f, e), e, e);                          // e + 3 e^2 / 4
+    return pd_fast_two_sum(y, pd_mul(pd_mul(0.5f, y), e));
+}
+
 // ---------------------------------------------------------------------------
 // pd_powf: deterministic x**y for x >= 0.
 //   log2(x) is formed in df32 from x = 2^e * m, m in [sqrt(1/2), sqrt(2)],

@@ -279,7 +279,7 @@ def test_error_free_transforms_are_exact():
         assert _frac(p[i]) + _frac(q[i]) == _frac(a[i]) * _frac(b[i])
 
 
-@pytest.mark.parametrize("op", ["add", "sub", "mul", "div", "sqrt", "recip"])
+@pytest.mark.parametrize("op", ["add", "sub", "mul", "div", "sqrt", "recip", "rsqrt"])
 def test_df32_operations_reach_double_float_accuracy(op):
     rng = np.random.default_rng(6)
     a64 = rng.uniform(0.1, 10.0, 5000)
@@ -292,7 +292,7 @@ def test_df32_operations_reach_double_float_accuracy(op):
     oh, ol = oracle.df_op(op, ah, al, bh, bl)
     got = W.join_df32(oh, ol)
     want = {"add": a_exact + b_exact, "sub": a_exact - b_exact, "mul": a_exact * b_exact,
-            "div": a_exact / b_exact, "sqrt": np.sqrt(a_exact), "recip": 1.0 / a_exact}[op]
+            "div": a_exact / b_exact, "sqrt": np.sqrt(a_exact), "recip": 1.0 / a_exact, "rsqrt": 1.0 / np.sqrt(a_exact)}[op]
     scale = np.maximum(np.abs(want), np.abs(a_exact) * 1e-3) if op == "sub" else np.abs(want)
     assert np.max(np.abs(got - want) / scale) < 2.0 ** -43
     assert np.all(np.abs(ol) <= np.spacing(np.abs(oh)))  # normalised pair
