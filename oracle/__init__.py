@@ -397,6 +397,16 @@ def kepler_rk4_f32(state, *, dt: float, gm: float = 1.0, steps: int) -> np.ndarr
     return out
 
 
+def pd_ctrl_pow(err, c) -> np.ndarray:
+    """(1 / err) ** c through the float routine the adaptive kernels' step controller uses."""
+    err, c = _f32(err), _f32(c)
+    err, c = np.broadcast_arrays(err, c)
+    err, c = np.ascontiguousarray(err), np.ascontiguousarray(c)
+    out = np.empty_like(err)
+    lib().orc_pd_ctrl_pow(_i64(err.size), _p(err, _f32p), _p(c, _f32p), _p(out, _f32p))
+    return out
+
+
 def pd_powf(x, y) -> np.ndarray:
     x, y = _f32(x), _f32(y)
     x, y = np.broadcast_arrays(x, y)

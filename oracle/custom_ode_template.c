@@ -54,7 +54,7 @@ void orc_custom_rk4(int64_t n, const float* const* in, float* const* out, int64_
 static inline float max_nan(float a, float b) { return (a != a) ? a : (b != b) ? b : (a > b ? a : b); }
 static inline float min_nan(float a, float b) { return (a != a) ? a : (b != b) ? b : (a < b ? a : b); }
 
-/* out: t, ORC_DIM states, steps, rejected, real.  pow_flavour 0: libm powf; 1: pd_powf. */
+/* out: t, ORC_DIM states, steps, rejected, real.  pow_flavour 0: libm powf on 1/err; 1: pd_ctrl_powers on err. */
 __attribute__((visibility("default")))
 void orc_custom_bs32(int64_t n, const float* const* in, float* const* out, double t1_, double rtol_, double atol_,
                      double dt0_, double pcoeff, double icoeff, double safety_, double fmin_, double fmax_,
@@ -71,7 +71,7 @@ void orc_custom_bs32(int64_t n, const float* const* in, float* const* out, doubl
             y3[ORC_DIM];
         for (int c = 0; c < ORC_DIM; ++c) y[c] = in[c][i];
         for (int c = 0; c < ORC_NPARAM; ++c) p[c] = in[ORC_DIM + c][i];
-        float t = 0.0f, dt = DT0, prev_inv_err = 1.0f, steps = 0.0f, rejected = 0.0f, real = 0.0f;
+        float t = 0.0f, dt = DT0, prev_inv_err = 1.0f, prev_err = 1.0f, steps = 0.0f, rejected = 0.0f, real = 0.0f;
         user_rhs(t, y, p, k1);
         for (int64_t it = 0; it < max_steps; ++it) {
             const int was_real = t < T1;
@@ -96,10 +96,13 @@ void orc_custom_bs32(int64_t n, const float* const* in, float* const* out, doubl
             err_norm = max_nan(err_norm, 1e-9f);
             const float inv_err = 1.0f / err_norm;
             float pa, pb;
-            if (pow_flavour == 1) { pa = pd_powf(inv_err, coeff1); pb = pd_powf(prev_inv_err, coeff2); }
-            else { pa = powf(inv_err, coeff1); pb = powf(prev_inv_err, coeff2); }
+            if (pow_flavour == 1) {
+                float unused;
+                pd_ctrl_powers(err_norm, coeff1, coeff1, &pa, &unused);
+                pd_ctrl_powers(prev_err, coeff2, coeff2, &pb, &unused);
+            } else { pa = powf(inv_err, coeff1); pb = powf(prev_inv_err, coeff2); }
             const float factor = (SAFETY * pa) * pb;
-            if (accept) prev_inv_err = inv_err;
+            if (accept) { prev_inv_err = inv_err; prev_err = err_norm; }
             dt = dt * min_nan(max_nan(factor, FMIN), FMAX);
             steps = steps + (accept ? 1.0f : 0.0f);
             rejected = rejected + (accept ? 0.0f : 1.0f);

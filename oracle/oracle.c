@@ -176,7 +176,7 @@ ORC_API void orc_lv_rk4_f64(int64_t n, const float* x0, const float* y0, const f
 /* Adaptive Bogacki-Shampine 3(2), FSAL, PI controller, Van der Pol            */
 /* (examples/02_adaptive_lockstep.py:69-171).  The loop runs the full          */
 /* max_steps trip count, stall iterations included, as the reference does.     */
-/* pow_flavour 0: C library powf; 1: the deterministic pd_powf.                */
+/* pow_flavour 0: C library powf on 1/err; 1: the deterministic pd_ctrl_powers. */
 /* ------------------------------------------------------------------------- */
 static inline float max_nan(float a, float b) { return (a != a) ? a : (b != b) ? b : (a > b ? a : b); }
 static inline float min_nan(float a, float b) { return (a != a) ? a : (b != b) ? b : (a < b ? a : b); }
@@ -197,7 +197,7 @@ ORC_API void orc_vdp_bs32(int64_t n, const float* x0_, const float* v0_, const f
         const float mu = mu_[i];
         float t = 0.0f, dt = DT0, x = x0_[i], v = v0_[i];
         float k1x = v, k1v = (mu * (1.0f - x * x)) * v - x;
-        float prev_inv_err = 1.0f, steps = 0.0f, rejected = 0.0f, real = 0.0f;
+        float prev_inv_err = 1.0f, prev_err = 1.0f, steps = 0.0f, rejected = 0.0f, real = 0.0f;
         for (int64_t it = 0; it < max_steps; ++it) {
             const int was_real = t < T1;
             dt = min_nan(dt, T1 - t);
@@ -220,10 +220,16 @@ ORC_API void orc_vdp_bs32(int64_t n, const float* x0_, const float* v0_, const f
             err_norm = max_nan(err_norm, 1e-9f);
             float inv_err = 1.0f / err_norm;
             float pa, pb;
-            if (pow_flavour == 1) { pa = pd_powf(inv_err, coeff1); pb = pd_powf(prev_inv_err, coeff2); }
-            else { pa = powf(inv_err, coeff1); pb = powf(prev_inv_err, coeff2); }
+            if (pow_flavour == 1) {
+                /* the same two powers, (1/err)**c1 and (1/prev_err)**c2, through the float routine the
+                 * CUDA kernel uses (it takes err, not 1/err) */
+                float unused;
+                pd_ctrl_powers(err_norm, coeff1, coeff1, &pa, &unused);
+                pd_ctrl_powers(prev_err, coeff2, coeff2, &pb, &unused);
+            } else { pa = powf(inv_err, coeff1); pb = powf(prev_inv_err, coeff2); }
             float factor = (SAFETY * pa) * pb;
             prev_inv_err = accept ? inv_err : prev_inv_err;
+            prev_err = accept ? err_norm : prev_err;
             dt = dt * min_nan(max_nan(factor, FMIN), FMAX);
             steps = steps + (accept ? 1.0f : 0.0f);
             rejected = rejected + (accept ? 0.0f : 1.0f);
@@ -482,6 +488,11 @@ ORC_API void orc_kepler_rk4_f32(int64_t n, const float* in, float* out, double d
 /* the deterministic pow, exposed so tests can compare it with double pow */
 ORC_API void orc_pd_powf(int64_t n, const float* x, const float* y, float* out) {
     for (int64_t i = 0; i < n; ++i) out[i] = pd_powf(x[i], y[i]);
+}
+
+/* the controller-grade power (1 / err) ** c, exposed for the same purpose */
+ORC_API void orc_pd_ctrl_pow(int64_t n, const float* err, const float* c, float* out) {
+    for (int64_t i = 0; i < n; ++i) { float unused; pd_ctrl_powers(err[i], c[i], c[i], &out[i], &unused); }
 }
 
 /* The C library's float functions on arrays, for the NumPy stand-in that runs the

@@ -159,6 +159,23 @@ def test_vdp_reference_configuration_counts_are_stable_across_pow():
     np.testing.assert_allclose(a[0], 10.0, atol=1e-4)
 
 
+def test_controller_powers_accuracy_and_domain():
+    """(1 / err) ** c for the step controller: float arithmetic only, within 8 ulp of
+    double precision over the range the error norm takes; exactly 1 at err = 1 (the
+    controller's initial state); pd_powf's rules outside the normal positive range."""
+    rng = np.random.default_rng(4)
+    err = np.exp(rng.uniform(np.log(1e-9), np.log(1e9), 400_000)).astype(np.float32)
+    for c in (0.7 / 3, -0.4 / 3, 0.5, -0.25):
+        got = oracle.pd_ctrl_pow(err, np.float32(c)).astype(np.float64)
+        want = (1.0 / err.astype(np.float64)) ** np.float64(np.float32(c))
+        ulp = np.abs(got - want) / want / 2.0 ** -24
+        assert ulp.max() < 8.0 and ulp.mean() < 2.0
+    assert oracle.pd_ctrl_pow(np.float32(1.0), np.float32(0.2333))[()] == 1.0
+    special = oracle.pd_ctrl_pow(np.array([0.0, np.inf, np.nan, 1e-42], np.float32), np.float32(0.25))
+    assert special[0] == np.inf and special[1] == 0.0 and np.isnan(special[2])
+    assert special[3] == np.inf      # 1 / err overflows for a subnormal err, as the reference's own 1 / err_norm does
+
+
 def test_pd_powf_accuracy_and_domain():
     rng = np.random.default_rng(1)
     x = np.exp(rng.uniform(np.log(1e-9), np.log(1e9), 200_000)).astype(np.float32)
