@@ -690,7 +690,13 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
         }
     }
 
-    const bool timed = knob(K_time_kernels) != 0;
+    // Kernel timing synchronises on an event, which a stream that is being captured into a graph cannot do.
+    bool timed = knob(K_time_kernels) != 0;
+    if (timed) {
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &capturing) != cudaSuccess) cudaGetLastError();
+        if (capturing != cudaStreamCaptureStatusNone) timed = false;
+    }
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     t_last_kernel_ms = -1.0;
     if (timed) {

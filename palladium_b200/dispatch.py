@@ -210,11 +210,15 @@ class BoundKernel:
         return call
 
     # ------------------------------------------------------------------ device-resident path
-    def launch_device(self, inputs, outputs=None, stream=None):
+    def launch_device(self, inputs, outputs=None, stream=None, workspace=None):
         """Launch on torch CUDA tensors, stream-ordered, without any host
         synchronisation or copy.  `inputs`: one tensor per kernel input, holding
         exactly the bytes of the traced operand.  Returns the output tensors
-        (allocated as uint8 byte buffers unless `outputs` is given)."""
+        (allocated as uint8 byte buffers unless `outputs` is given).
+        `workspace`: a uint8 CUDA tensor of at least `scratch_bytes` (see
+        `pd_explain`) for the kernels' scratch, in place of the library's own
+        per-stream pool -- a caller that records launches into a CUDA graph owns
+        the memory the graph keeps pointing at this way."""
         torch = _require_cuda()
         spec = self.spec
         if len(inputs) != len(spec.inputs):
@@ -238,6 +242,7 @@ class BoundKernel:
             [(t.data_ptr(), b) for t, b in zip(inputs, in_bytes)],
             [(t.data_ptr(), b) for t, b in zip(outputs, out_bytes)],
             stream=st.cuda_stream,
+            workspace=(workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None else None,
         )
         return outputs
 

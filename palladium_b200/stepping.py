@@ -63,6 +63,16 @@ class Stepper:
             sizes = [max(int(np.prod(o.array_shape)) * o.dtype.itemsize, 1) for o in spec.outputs]
             # two output sets: a launch never writes the buffers it reads
             self._spare = [[torch.empty(s, dtype=torch.uint8, device="cuda") for s in sizes] for _ in range(2)]
+            # The kernels' scratch (ping-pong fields of a multi-step stencil call, queue heads, partial
+            # sums) belongs to this object rather than to the library's per-stream pool: a captured
+            # graph keeps the pointer, and the pool may free and re-allocate its buffer when another
+            # call on a stream with the same handle needs more.
+            from . import _native
+
+            info = _native.explain(spec.family.family_id, spec.params, self._bound.math_mode, spec.grid,
+                                   self._bound.threadgroup)
+            self._workspace = (torch.empty(int(info.scratch_bytes) + 256, dtype=torch.uint8, device="cuda")
+                               if info.scratch_bytes > 0 else None)
         self._which = 0
         self._outputs = None
         self._start = torch.cuda.Event(enable_timing=True)
@@ -71,6 +81,13 @@ class Stepper:
         self._graph = None
         self._graph_which = 0
         self.launches = 0
+
+    def _aligned_workspace(self):
+        """The workspace from its first 256-byte boundary on (the native call requires that alignment)."""
+        if self._workspace is None:
+            return None
+        offset = (-self._workspace.data_ptr()) % 256
+        return self._workspace[offset:]
 
     @staticmethod
     def _bind(call, arrs) -> BoundKernel:
@@ -101,7 +118,7 @@ class Stepper:
                 # Alternate between the two output sets: after this launch the fed
                 # inputs alias set `which`, so the next launch must write the other.
                 outs = self._spare[self._which]
-                self._bound.launch_device(self._inputs, outs, stream=self._stream)
+                self._bound.launch_device(self._inputs, outs, stream=self._stream, workspace=self._aligned_workspace())
                 for k, slot in enumerate(self._feedback):
                     self._inputs[slot] = outs[k]
                 self._which = 1 - self._which
@@ -134,7 +151,7 @@ class Stepper:
             with torch.cuda.graph(g, stream=self._stream):
                 for _ in range(2):
                     outs = self._spare[self._which]
-                    self._bound.launch_device(self._inputs, outs, stream=self._stream)
+                    self._bound.launch_device(self._inputs, outs, stream=self._stream, workspace=self._aligned_workspace())
                     for k, slot in enumerate(self._feedback):
                         self._inputs[slot] = outs[k]
                     self._which = 1 - self._which
