@@ -1,7 +1,7 @@
 """Benchmark of the ensemble-integrator hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload rk4_lv|vdp_bs32|gbm|gray_scott|kepler_df32|custom_ode] [--n N_PER_GPU]
+                    [--workload rk4_lv|vdp_bs32|gbm|gray_scott|kepler_df32|custom_ode|host_copies] [--n N_PER_GPU]
 
 One "step" is one pass of a kernel family over one batch of synthetic input.
 The default workload is the headline one: the fixed-step RK4 Lotka-Volterra

@@ -571,7 +571,7 @@ def multi_gpu_gray_scott(rank: int, world: int, barrier, max_over_ranks, math_mo
                          halo: int = 16, steps_per_pass: int = 64, iters: int = 3) -> dict:
     """The stencil on `world` GPUs: row slabs on a periodic ring, boundary rows
     stored into the neighbours' ghost rows by the compute kernel (peer stores
-    over NVLink, no multicast, nothing waits inside a kernel).  16384 x 16384 on 8
+    over NVLink, every copy engine load is an ordinary single-CTA one, nothing waits inside a kernel).  16384 x 16384 on 8
     GPUs (2048 rows per GPU); 8192 rows x 16384 columns per GPU otherwise.
     Checked in the same run: a 1024 x 16384 grid advanced 32 steps under SAFE by
     the slabs against rank 0 advancing the whole grid alone."""
@@ -646,6 +646,88 @@ def multi_gpu_summary(rank: int, world: int, barrier, max_over_ranks, math_mode:
         except Exception as exc:   # every rank takes the same path: the failure is reported, the headline still prints
             out[name] = {"error": f"{type(exc).__name__}: {exc}"}
     return out
+
+
+# ----------------------------------------------------------------------------- host <-> device copy ceiling
+def host_copy_rates(rank: int, world: int, n_in: int = 100 << 20, n_out: int = 32 << 20, reps: int = 8) -> dict:
+    """What the host-buffer path can at best achieve on this machine: plain
+    cudaMemcpyAsync rates from / to pinned buffers of the sizes one RK4 pass moves
+    (100 MB up, 32 MB down), per rank alone (the other ranks idle) and with every rank
+    copying at once, each direction by itself and both together; then the
+    host-buffer call itself with every rank calling at once.  Every rank takes part;
+    the returned dict holds one list per figure, indexed by rank (on every rank)."""
+    import torch
+    import torch.distributed as dist
+
+    from palladium_b200 import cuda_call_jit, families
+    from palladium_b200 import workloads as W
+
+    hin = torch.empty(n_in, dtype=torch.uint8).pin_memory()
+    hin.fill_(1)
+    hout = torch.empty(n_out, dtype=torch.uint8).pin_memory()
+    hout.fill_(1)
+    din = torch.empty(n_in, dtype=torch.uint8, device="cuda")
+    dout = torch.empty(n_out, dtype=torch.uint8, device="cuda")
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def h2d():
+        din.copy_(hin, non_blocking=True)
+
+    def d2h():
+        hout.copy_(dout, non_blocking=True)
+
+    def both():
+        with torch.cuda.stream(up):
+            din.copy_(hin, non_blocking=True)
+        with torch.cuda.stream(down):
+            hout.copy_(dout, non_blocking=True)
+
+    def rate(fn, nbytes):   # GB/s over `reps` back-to-back copies
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        torch.cuda.synchronize()
+        return nbytes * reps / (time.perf_counter() - t0) / 1e9
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    res = {}
+    for r in range(world):          # one rank at a time
+        sync()
+        if r == rank:
+            res["alone_h2d_gbs"], res["alone_d2h_gbs"] = rate(h2d, n_in), rate(d2h, n_out)
+            res["alone_both_gbs"] = rate(both, n_in + n_out)
+    sync()
+    res["all_ranks_h2d_gbs"] = rate(h2d, n_in)
+    sync()
+    res["all_ranks_d2h_gbs"] = rate(d2h, n_out)
+    sync()
+    res["all_ranks_both_gbs"] = rate(both, n_in + n_out)
+    sync()
+    n = 1 << 22
+    call = cuda_call_jit(families.lv_rk4(0.01, 1000), grid=(n,), out_shape=(_shaped((n,)), _shaped((n,))),
+                         math_mode="fast")
+    np_in = [torch.from_numpy(a).pin_memory().numpy() for a in W.lotka_volterra_ensemble(n, seed=17 + rank)]
+    for _ in range(2):
+        call(*np_in)
+    sync()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        call(*np_in)
+    res["host_buffer_call_ms_all_ranks"] = (time.perf_counter() - t0) / reps * 1e3
+    res["host_buffer_call_gbs"] = (sum(a.nbytes for a in np_in) + 8 * n) / (res["host_buffer_call_ms_all_ranks"] * 1e-3) / 1e9
+    sync()
+    if world > 1:
+        everyone = [None] * world
+        dist.all_gather_object(everyone, res)
+    else:
+        everyone = [res]
+    return {k: [round(float(e[k]), 2) for e in everyone] for k in res}
 
 
 # ----------------------------------------------------------------------------- as the main workload
@@ -753,6 +835,13 @@ def run(args, rank: int, local_rank: int, world: int, barrier, max_over_ranks) -
                      "roofline": {"bound": "fp32_fma", "achieved": r["trajectory_steps_per_s"] * 58 / 1e12,
                                   "peak": fma_peak / 1e12, "unit": "TFLOP/s", "frac": r.get("frac_of_fp32_peak"),
                                   "traffic": None}})
+    elif name == "host_copies":
+        rates = host_copy_rates(rank, world)
+        total = sum(rates["host_buffer_call_gbs"])
+        line.update({"metric": "host_buffer_call_bytes_per_s", "value": total * 1e9, "unit": "B/s", "scaling": "weak",
+                     "ms_per_step": max(rates["host_buffer_call_ms_all_ranks"]), "dtype": "u8", "gpu_launches": None,
+                     "config": {"workload": "host <-> device copy rates behind the host-buffer call, per rank",
+                                "bytes_up_per_pass": 100 << 20, "bytes_down_per_pass": 32 << 20, **rates}})
     elif name == "full":
         line.update(full_configs(fma_peak, int_peak))
     else:
