@@ -217,6 +217,7 @@ struct Plan {
     int64_t launches = 1;
     int64_t scratch_bytes = 0;
     int variant = 0;
+    int64_t dynamic_smem = 0;      // bytes of dynamic shared memory per block (the tiled stencil kernels)
     const void* kernel = nullptr;
     PdRtcKernel rtc;               // run-time compiled families only
 };
@@ -234,9 +235,12 @@ int check_block(int b, char* err, size_t err_cap) {
     return PD_OK;
 }
 
-int occupancy_blocks(const void* kernel, int block) {
+int occupancy_blocks(const void* kernel, int block, size_t dynamic_smem = 0) {
     int n = 0;
-    if (!kernel || cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, block, 0) != cudaSuccess) {
+    if (dynamic_smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dynamic_smem) != cudaSuccess)
+        cudaGetLastError();
+    if (!kernel || cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, block, dynamic_smem) != cudaSuccess) {
         cudaGetLastError();
         return 0;
     }
@@ -497,6 +501,12 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
                     {"pd_gs_rt_kernel<2>", "pd_gs_rt_kernel<3>", "pd_gs_rt_kernel<4>"}};
                 plan->kernel_name = names[form][k - 2];
                 plan->items = 4;  // cells per thread per row
+                {
+                    // shared memory per block: the block-tile kernels keep two (three when persistent) copies of
+                    // a (16 + 2k) x 128 tile of both fields; the register-tile kernel one landing zone per warp
+                    const int64_t tile = 2 * (int64_t)(form == 2 ? PD_GS_RT_ROWS + 2 * k : PD_GS_TB_ROWS + 2 * k) * 512;
+                    plan->dynamic_smem = form == 2 ? PD_GS_RT_WARPS * tile + 8 * PD_GS_RT_WARPS : (form == 1 ? 3 : 2) * tile;
+                }
                 if (form == 2) {
                     plan->block[0] = PD_GS_RT_WARPS * 32;
                     int64_t g = (int64_t)dev.sms * PD_GS_RT_BLOCKS;
@@ -1306,7 +1316,7 @@ int pd_explain(int family, const void* params, size_t params_bytes, int math_mod
     info->scratch_bytes = plan.scratch_bytes;
     info->regs_per_thread = -1;
     info->static_smem_bytes = -1;
-    info->dynamic_smem_bytes = 0;
+    info->dynamic_smem_bytes = (int32_t)plan.dynamic_smem;
     info->blocks_per_sm = -1;
     if (dev.present && plan.rtc.function) {
         info->regs_per_thread = plan.rtc.regs;
@@ -1319,7 +1329,7 @@ int pd_explain(int family, const void* params, size_t params_bytes, int math_mod
             info->regs_per_thread = attr.numRegs;
             info->static_smem_bytes = (int32_t)attr.sharedSizeBytes;
             const int threads = (int)(plan.block[0] * plan.block[1] * plan.block[2]);
-            info->blocks_per_sm = occupancy_blocks(plan.kernel, threads);
+            info->blocks_per_sm = occupancy_blocks(plan.kernel, threads, (size_t)plan.dynamic_smem);
         } else {
             cudaGetLastError();
         }
