@@ -124,3 +124,56 @@ def test_df32_non_finite_inputs_match_the_oracle():
     want = oracle.lv_rk4_df32(*args, dt=0.01, steps=20)
     np.testing.assert_array_equal(got[0], want[0])
     np.testing.assert_array_equal(got[1], want[1])
+
+
+# The SAFE adaptive kernels divide with pd_div_nonneg, a correctly rounded sequence
+# without the compiler's data-dependent slow path; every quotient must equal the
+# IEEE division's bit for bit.  A caller-written kernel (pd_math.h is in scope)
+# compares the two on the device: per thread REPS operand pairs drawn from Threefry
+# bits, the mismatches counted.
+DIV_CHECK = r'''
+extern "C" __global__ void div_check(const uint32_t* key, const uint32_t* range, uint32_t* bad,
+                                     long long gx, long long gy, long long gz) {
+    const long long i = PD_THREAD_X;
+    if (i >= gx) return;
+    const pd_u32x2 k = pd_fold_in(key[0], key[1], (uint32_t)i);
+    // exponent fields: a in [range[0], range[0] + range[1]), b in [range[2], range[2] + range[3])
+    const uint32_t a_lo = range[0], a_n = range[1], b_lo = range[2], b_n = range[3], reps = range[4];
+    uint32_t count = 0;
+    for (uint32_t rep = 0; rep < reps; ++rep) {
+        const uint32_t ra = pd_random_bits(k.a, k.b, 3u * rep), rb = pd_random_bits(k.a, k.b, 3u * rep + 1u);
+        const uint32_t rc = pd_random_bits(k.a, k.b, 3u * rep + 2u);
+        uint32_t ma = ra & 0x007FFFFFu, mb = rb & 0x007FFFFFu;
+        // one pair in four gets a significand that is hard for division: all ones, a single bit, or zero
+        if ((rc & 3u) == 0u) ma = (rc & 4u) ? 0x007FFFFFu : ((rc & 8u) ? 0u : 1u << ((rc >> 8) % 23u));
+        if ((rc & 48u) == 0u) mb = (rc & 64u) ? 0x007FFFFFu : ((rc & 128u) ? 0u : 1u << ((rc >> 16) % 23u));
+        const float a = pd_u2f(((a_lo + (ra >> 23) % a_n) << 23) | ma);
+        const float b = pd_u2f(((b_lo + (rb >> 23) % b_n) << 23) | mb);
+        count += pd_f2u(pd_div_nonneg(a, b)) != pd_f2u(__fdiv_rn(a, b)) ? 1u : 0u;
+    }
+    // the special values, once per thread: zero numerators, and operands outside the stated range
+    const float special[8] = {0.0f, 1e-42f, 3e38f, 1.0f, pd_u2f(0x7F800000u), pd_u2f(0x7FC00000u), -1.0f, 1e-30f};
+    for (int p = 0; p < 8; ++p)
+        for (int q = 0; q < 8; ++q) {
+            const uint32_t want = pd_f2u(__fdiv_rn(special[p], special[q])), got = pd_f2u(pd_div_nonneg(special[p], special[q]));
+            const bool both_nan = (want & 0x7FFFFFFFu) > 0x7F800000u && (got & 0x7FFFFFFFu) > 0x7F800000u;
+            count += (want != got && !both_nan) ? 1u : 0u;
+        }
+    bad[i] = count;
+}
+'''
+
+
+@pytest.mark.parametrize("name,a_lo,a_n,b_lo,b_n", [
+    ("the whole stated range: a in [2^-104, 2^60), b in [2^-60, 2^20)", 23, 164, 67, 80),
+    ("error-norm operands: a in [2^-50, 2^-10), b in [2^-30, 2^-5)", 77, 40, 97, 25),
+    ("beyond the range on both sides (the IEEE division itself)", 1, 253, 1, 253),
+])
+def test_safe_division_equals_ieee_division_bit_for_bit(name, a_lo, a_n, b_lo, b_n):
+    from palladium_b200 import families, pl
+
+    threads, reps = 1 << 20, 2048        # 2.1e9 operand pairs per case
+    call = pd.cuda_call(families.source_kernel(DIV_CHECK, "div_check"), grid=(threads,),
+                        out_shape=pl.ShapeDtypeStruct((threads,), np.uint32), math_mode=SAFE)
+    bad = call(W.gbm_key(11), np.array([a_lo, a_n, b_lo, b_n, reps], np.uint32))
+    assert int(bad.sum()) == 0, f"{int(bad.sum())} of {threads * reps} quotients differ: {name}"
