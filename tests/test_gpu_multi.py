@@ -59,6 +59,18 @@ def _worker(rank, world, port, out_dir):
         assert pushed.exchanges == 1 and pushed.pushes == -(-steps // halo)
         pushed.close()
         assert torch.equal(pu, results[0][0]) and torch.equal(pv, results[0][1])
+        # the same with the register-tile kernel (tiles fetched by the copy engine) doing the pushing,
+        # forced here because the planner gives a grid this small to the block-tile kernel
+        from palladium_b200 import _native
+
+        with _native.thread_tuning(gs_persistent=2):
+            pushed = sharded.GrayScottSlab(torch.from_numpy(u0[lo:hi]).cuda(), torch.from_numpy(v0[lo:hi]).cuda(), rows,
+                                           halo=halo, constants=dict(oracle.GS_DEFAULTS), math_mode="safe", push=True)
+            pushed.advance(steps)
+            ru, rv = (t.clone() for t in pushed.owned())
+            pushed.close()
+        assert torch.equal(ru, results[0][0]) and torch.equal(rv, results[0][1])
+        assert _native.device_status() == 0
         u, v = results[0]
         cfg = dict(s0=100.0, strike=100.0, r=0.05, sigma=0.2, t=1.0, steps=64)
         res = sharded.gbm_monte_carlo(W.gbm_key(0), 100_003, cfg, math_mode="safe")
