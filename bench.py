@@ -353,7 +353,7 @@ def main():
            "h2d_bytes_per_step": int(sum(a.nbytes for a in np_in)), "d2h_bytes_per_step": int(8 * n),
            "ms_per_step": e2e_ms, "steps": e2e_steps, "checksum": checksum,
            "path": "cuda_call_jit(host arrays) -> pd_dispatch_host: pinned host inputs and outputs; the call cuts the "
-                   "ensemble into ~32 chunks over 3 streams so upload, kernel and download overlap"}
+                   "ensemble into ~32 chunks over 6 streams so upload, kernel and download overlap"}
 
     # ---- named configuration (N = 100 000), device-resident ---------------------------
     named = None
