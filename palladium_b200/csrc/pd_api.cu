@@ -52,7 +52,7 @@ int fail(int code, char* err, size_t cap, const char* fmt, ...) {
     X(lv_block, 0)             /* 0 = choose from N */                                                          \
     X(vdp_variant, 2)          /* 0 direct, 1 lane refill, 2 refill + tail compaction, 3 two passes */           \
     X(vdp_block, 128)                                                                                            \
-    X(vdp_refill_every, 8)     /* attempts between refill checks */                                             \
+    X(vdp_refill_every, 16)    /* attempts between refill checks (16 measured 3 % faster than 8, 24 no better) */                                             \
     X(vdp_pass_limit, 1000)    /* variant 3: attempts after which pass one suspends a trajectory */             \
     X(vdp_pass_limit2, 0)      /* variant 3: cap of a second suspending pass (0 = none) */                      \
     X(vdp_pass_limit3, 0)      /* variant 3: cap of a third suspending pass (0 = none) */                       \
