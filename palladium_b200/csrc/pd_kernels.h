@@ -18,6 +18,8 @@ struct PdLvArgs {
     int64_t n;
     int steps;
     float h_half, h_full, h_sixth;
+    int packed;   // two trajectories per packed f32x2 operation (kernels with 2 or 4 trajectories per thread)
+    float neg_zero;   // -0.0f, as a run-time value (see p_mad in pd_kernels.cu)
 };
 
 struct PdVdpArgs {

@@ -82,6 +82,40 @@ def test_lv_rk4_items_per_thread_agree(items):
     np.testing.assert_array_equal(got[1], want[1])
 
 
+@pytest.mark.parametrize("items", [2, 4])
+@pytest.mark.parametrize("n", [10_007, 4099, 2, 3])
+def test_lv_rk4_packed_pairs_safe_bit_exact(items, n):
+    """Two trajectories per packed f32x2 instruction.  SAFE does not choose this form (it measured
+    slower than scalar code), but it stays selectable and must round every product and sum on its
+    own: the assembler contracts a packed multiply with the packed add that consumes it, so the
+    kernel gives every such product an add of -0 to be contracted with instead."""
+    from palladium_b200 import _native
+
+    args = W.lotka_volterra_ensemble(n)
+    with _native.thread_tuning(lv_items_per_thread=items, lv_packed=1):
+        got = H.lv_solver(n, steps=200, math_mode=SAFE)(*args)
+    want = oracle.lv_rk4(*args, dt=0.01, steps=200)
+    np.testing.assert_array_equal(got[0], want[0])
+    np.testing.assert_array_equal(got[1], want[1])
+
+
+@pytest.mark.parametrize("packed", [0, 1])
+@pytest.mark.parametrize("items", [2, 4])
+@pytest.mark.parametrize("mode", [RELAXED, FAST])
+def test_lv_rk4_packed_and_scalar_meet_the_same_bar(mode, items, packed):
+    from palladium_b200 import _native
+
+    n = 50_001
+    args = W.lotka_volterra_ensemble(n)
+    with _native.thread_tuning(lv_items_per_thread=items, lv_packed=packed):
+        got = H.lv_solver(n, steps=1000, math_mode=mode)(*args)
+    want = oracle.lv_rk4(*args, dt=0.01, steps=1000)
+    for g, w in zip(got, want):
+        rel = np.abs(g - w) / np.maximum(np.abs(w), 1e-6)
+        assert np.mean(rel <= 1e-5) >= 0.95
+        assert rel.max() <= 1e-4
+
+
 def test_rk4_named_configuration_safe_is_bit_exact():
     """The benchmark configuration itself -- N = 100 000, dt = 0.01, 1000 steps,
     final state as one (N, 2) array -- under SAFE: every state equals the oracle's
