@@ -101,6 +101,30 @@ def bench_vdp(n: int, math_mode="relaxed", warmup: int = 1, iters: int = 3, fma_
     return res
 
 
+VDP_RHS = "dy[0] = y[1];\ndy[1] = (p[0]*(1.0f - y[0]*y[0]))*y[1] - y[0];"
+
+
+def bench_vdp_pair(n: int, method: str = "tsit5", math_mode="safe", warmup: int = 1, iters: int = 3) -> dict:
+    """The Van der Pol configuration of `bench_vdp` (same ensemble, t1 and tolerances) through
+    `custom_ode` with a seven-stage 5(4) pair: what the same job costs with the method the
+    reference's CPU comparison integrates with."""
+    import torch
+
+    from palladium_b200 import cuda_call_jit, families
+    from palladium_b200 import workloads as W
+
+    cfg = {k: v for k, v in W.VDP_CONFIG.items() if k not in ("n", "seed", "error_order")}
+    call = cuda_call_jit(families.custom_ode(VDP_RHS, 2, 1, method=method, **cfg), grid=(n,),
+                         out_shape=tuple(_shaped((n,)) for _ in range(6)), math_mode=math_mode)
+    dev = [torch.from_numpy(a).cuda() for a in W.van_der_pol_ensemble(n)]
+    out = call(*dev)
+    ms = _time(lambda: call(*dev), warmup, iters)
+    attempts = float((out[4].double() + out[5].double()).sum())
+    return {"workload": f"adaptive {method} Van der Pol (custom_ode)", "trajectories": n, "math_mode": str(math_mode),
+            "ms": ms, "attempts": attempts, "attempts_per_s": attempts / (ms * 1e-3), "mean_attempts": attempts / n,
+            "all_reached_t1": bool((out[0] == cfg["t1"]).all()), "trajectories_per_s": n / (ms * 1e-3)}
+
+
 def bench_gbm(n: int, math_mode="fast", warmup: int = 1, iters: int = 3, int_peak: float | None = None) -> dict:
     import torch
 
@@ -257,6 +281,7 @@ def quick_summary(named: bool = True) -> dict:
     out["kepler_df32"] = bench_kepler(1 << 20, 100, fma_peak=fma_peak)
     out["lv_df32"] = bench_lv_df32(1 << 20, 100, fma_peak=fma_peak)
     out["custom_ode_lv"] = bench_custom_ode(1 << 22, 1000, "fast", fma_peak=fma_peak)
+    out["vdp_tsit5_safe"] = bench_vdp_pair(1 << 18, "tsit5", "safe")
     out.update(named_rk4_modes(fma_peak))
     if named:
         out.update(named_configs(fma_peak, int_peak))

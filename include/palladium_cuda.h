@@ -159,10 +159,16 @@ typedef struct pd_threefry_params {
  *   method PD_ODE_BS32: Bogacki-Shampine 3(2) with the PI controller, counters
  *     and stall semantics of the Van der Pol family.
  *     in: as above.  out: t, dim state arrays, steps, rejected, real, (N) f32.
+ *   method PD_ODE_DOPRI5, PD_ODE_TSIT5: the seven-stage 5(4) pairs of Dormand and
+ *     Prince and of Tsitouras (the pair the reference's CPU comparison runs,
+ *     benchmarks/bench_ensembles.py:88-118) under the same controller, counters
+ *     and outputs as PD_ODE_BS32; error_order is 5 for them.
  * Compiler errors in the right-hand side come back as PD_ERR_INVALID_ARGUMENT
  * with the compiler's log in `err`. */
 #define PD_ODE_RK4 0
 #define PD_ODE_BS32 1
+#define PD_ODE_DOPRI5 2
+#define PD_ODE_TSIT5 3
 #define PD_ODE_MAX_DIM 8
 #define PD_ODE_MAX_PARAM 8
 typedef struct pd_custom_ode_params {
@@ -170,7 +176,7 @@ typedef struct pd_custom_ode_params {
     int64_t dim, nparam, method;
     double dt;                /* RK4 */
     int64_t steps;
-    double t1, rtol, atol, dt0;   /* BS3(2) */
+    double t1, rtol, atol, dt0;   /* the adaptive methods */
     double pcoeff, icoeff, safety, factor_min, factor_max;
     int64_t error_order;
     int64_t max_steps;

@@ -79,3 +79,42 @@ def bs32(rhs: str, dim: int, nparam: int, arrays, *, pow: str = "libm", **params
        d(cfg["factor_max"]), ctypes.c_int64(cfg["error_order"]), ctypes.c_int64(cfg["max_steps"]),
        ctypes.c_int({"libm": 0, "pd": 1}[pow]))
     return tuple(outs)
+
+
+ERK_METHODS = {"dopri5": 2, "tsit5": 3}
+
+
+def erk(rhs: str, dim: int, nparam: int, arrays, *, method: str, pow: str = "libm", **params):
+    """(t, states..., steps, rejected, real) of the adaptive loop around a seven-stage 5(4) pair
+    ("dopri5" or "tsit5"); `error_order` defaults to 5."""
+    cfg = dict(BS32_DEFAULTS, error_order=5)
+    cfg.update(params)
+    ins = [np.ascontiguousarray(a, np.float32) for a in arrays]
+    assert len(ins) == dim + nparam
+    n = ins[0].size
+    outs = [np.empty(n, np.float32) for _ in range(dim + 4)]
+    fn = _lib(rhs, dim, nparam).orc_custom_erk
+    fn.restype = None
+    d = ctypes.c_double
+    fn(ctypes.c_int64(n), _pointers(ins), _pointers(outs), ctypes.c_int(ERK_METHODS[method]), d(cfg["t1"]),
+       d(cfg["rtol"]), d(cfg["atol"]), d(cfg["dt0"]), d(cfg["pcoeff"]), d(cfg["icoeff"]), d(cfg["safety"]),
+       d(cfg["factor_min"]), d(cfg["factor_max"]), ctypes.c_int64(cfg["error_order"]),
+       ctypes.c_int64(cfg["max_steps"]), ctypes.c_int({"libm": 0, "pd": 1}[pow]))
+    return tuple(outs)
+
+
+def tableau(method: str):
+    """(A, c, e) of a 5(4) pair as float64 arrays, read back from the coefficients the compiled
+    oracle holds (float32 values): A is 7 x 7 strictly lower triangular with the weights as its
+    last row."""
+    lib = _lib("dy[0] = y[0];", 1, 0)
+    fn = lib.orc_tableau
+    fn.restype = None
+    a = np.zeros((6, 6), np.float32)
+    c = np.zeros(7, np.float32)
+    e = np.zeros(7, np.float32)
+    fp = ctypes.POINTER(ctypes.c_float)
+    fn(ctypes.c_int(ERK_METHODS[method]), a.ctypes.data_as(fp), c.ctypes.data_as(fp), e.ctypes.data_as(fp))
+    full = np.zeros((7, 7))
+    full[1:, :6] = a
+    return full, c.astype(np.float64), e.astype(np.float64)

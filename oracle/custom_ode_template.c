@@ -10,7 +10,13 @@
  *   - the adaptive Bogacki-Shampine 3(2) loop with PI controller of
  *     examples/02_adaptive_lockstep.py:69-171, run for the full max_steps
  *     iterations as the reference runs it (no early exit here).
- * On the reference's own two systems these loops equal the pinned family
+ *   - the same adaptive loop around the seven-stage 5(4) pairs of Dormand-Prince
+ *     and Tsitouras (coefficients in pd_math.h).  The reference has no kernel
+ *     of these, only a CPU comparison that runs diffrax's Tsit5
+ *     (benchmarks/bench_ensembles.py:88-118): parity unpinned; what pins the
+ *     coefficients is the order conditions and a float64 solution
+ *     (tests/test_oracle.py).
+ * On the reference's own two systems the first two loops equal the pinned family
  * oracles bit for bit; for other systems parity is unpinned (the reference has
  * nothing to compare with).
  */
@@ -114,4 +120,86 @@ void orc_custom_bs32(int64_t n, const float* const* in, float* const* out, doubl
         out[ORC_DIM + 2][i] = rejected;
         out[ORC_DIM + 3][i] = real;
     }
+}
+
+/* method 2: Dormand-Prince 5(4); 3: Tsitouras 5(4).  Same outputs and controller as orc_custom_bs32 with
+ * pow_flavour as there.  A stage sums its non-zero coefficients left to right. */
+__attribute__((visibility("default")))
+void orc_custom_erk(int64_t n, const float* const* in, float* const* out, int method, double t1_, double rtol_,
+                    double atol_, double dt0_, double pcoeff, double icoeff, double safety_, double fmin_,
+                    double fmax_, int64_t error_order, int64_t max_steps, int pow_flavour) {
+    static const float A_dp[6][6] = PD_DOPRI5_A, A_ts[6][6] = PD_TSIT5_A;
+    static const float C_dp[7] = PD_DOPRI5_C, C_ts[7] = PD_TSIT5_C;
+    static const float E_dp[7] = PD_DOPRI5_E, E_ts[7] = PD_TSIT5_E;
+    const float (*A)[6] = method == 2 ? A_dp : A_ts;
+    const float* C = method == 2 ? C_dp : C_ts;
+    const float* E = method == 2 ? E_dp : E_ts;
+    const float T1 = (float)t1_, RTOL = (float)rtol_, ATOL = (float)atol_, DT0 = (float)dt0_;
+    const float SAFETY = (float)safety_, FMIN = (float)fmin_, FMAX = (float)fmax_;
+    const float coeff1 = (float)((icoeff + pcoeff) / (double)error_order);
+    const float coeff2 = (float)(-pcoeff / (double)error_order);
+#pragma omp parallel for schedule(dynamic, 4)
+    for (int64_t i = 0; i < n; ++i) {
+        float y[ORC_DIM], p[ORC_NPARAM_ALLOC], k[7][ORC_DIM], w[ORC_DIM];
+        for (int c = 0; c < ORC_DIM; ++c) y[c] = in[c][i];
+        for (int c = 0; c < ORC_NPARAM; ++c) p[c] = in[ORC_DIM + c][i];
+        float t = 0.0f, dt = DT0, prev_inv_err = 1.0f, prev_err = 1.0f, steps = 0.0f, rejected = 0.0f, real = 0.0f;
+        user_rhs(t, y, p, k[0]);
+        for (int64_t it = 0; it < max_steps; ++it) {
+            const int was_real = t < T1;
+            dt = min_nan(dt, T1 - t);
+            for (int s = 1; s < 7; ++s) {
+                for (int c = 0; c < ORC_DIM; ++c) {
+                    float acc = A[s - 1][0] * k[0][c];
+                    for (int j = 1; j < s; ++j)
+                        if (A[s - 1][j] != 0.0f) acc = acc + A[s - 1][j] * k[j][c];
+                    w[c] = y[c] + dt * acc;
+                }
+                user_rhs(t + C[s] * dt, w, p, k[s]);
+            }
+            float err_norm = 0.0f;
+            for (int c = 0; c < ORC_DIM; ++c) {
+                float e = E[0] * k[0][c];
+                for (int j = 1; j < 7; ++j)
+                    if (E[j] != 0.0f) e = e + E[j] * k[j][c];
+                const float ratio = fabsf(dt * e) / (ATOL + RTOL * fabsf(w[c]));
+                err_norm = c == 0 ? ratio : max_nan(err_norm, ratio);
+            }
+            const int accept = err_norm <= 1.0f;
+            if (accept) {
+                t = t + dt;
+                for (int c = 0; c < ORC_DIM; ++c) { y[c] = w[c]; k[0][c] = k[6][c]; }
+            }
+            err_norm = max_nan(err_norm, 1e-9f);
+            const float inv_err = 1.0f / err_norm;
+            float pa, pb;
+            if (pow_flavour == 1) {
+                float unused;
+                pd_ctrl_powers(err_norm, coeff1, coeff1, &pa, &unused);
+                pd_ctrl_powers(prev_err, coeff2, coeff2, &pb, &unused);
+            } else { pa = powf(inv_err, coeff1); pb = powf(prev_inv_err, coeff2); }
+            const float factor = (SAFETY * pa) * pb;
+            if (accept) { prev_inv_err = inv_err; prev_err = err_norm; }
+            dt = dt * min_nan(max_nan(factor, FMIN), FMAX);
+            steps = steps + (accept ? 1.0f : 0.0f);
+            rejected = rejected + (accept ? 0.0f : 1.0f);
+            real = real + ((was_real && accept) ? 1.0f : 0.0f);
+        }
+        out[0][i] = t;
+        for (int c = 0; c < ORC_DIM; ++c) out[1 + c][i] = y[c];
+        out[ORC_DIM + 1][i] = steps;
+        out[ORC_DIM + 2][i] = rejected;
+        out[ORC_DIM + 3][i] = real;
+    }
+}
+
+/* The coefficients as compiled, for the order-condition test. */
+__attribute__((visibility("default")))
+void orc_tableau(int method, float* a36, float* c7, float* e7) {
+    static const float A_dp[6][6] = PD_DOPRI5_A, A_ts[6][6] = PD_TSIT5_A;
+    static const float C_dp[7] = PD_DOPRI5_C, C_ts[7] = PD_TSIT5_C;
+    static const float E_dp[7] = PD_DOPRI5_E, E_ts[7] = PD_TSIT5_E;
+    for (int s = 0; s < 6; ++s)
+        for (int j = 0; j < 6; ++j) a36[s * 6 + j] = method == 2 ? A_dp[s][j] : A_ts[s][j];
+    for (int j = 0; j < 7; ++j) { c7[j] = method == 2 ? C_dp[j] : C_ts[j]; e7[j] = method == 2 ? E_dp[j] : E_ts[j]; }
 }

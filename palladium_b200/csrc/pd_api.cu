@@ -374,7 +374,7 @@ int build_plan(int family, const void* params, size_t params_bytes, int math_mod
             plan->kernel_name = pd_rtc_kernel_name(p);
             plan->block[0] = b;
             plan->grid[0] = (n + b - 1) / b;
-            if (p->method == PD_ODE_BS32) {
+            if (p->method != PD_ODE_RK4) {
                 // persistent warps, about 1024 threads per SM (as for the Van der Pol kernel)
                 int per_sm = 1024 / b > 0 ? 1024 / b : 1;
                 int64_t g = (int64_t)dev.sms * per_sm;
@@ -961,7 +961,7 @@ int launch_impl(int family, const void* params, size_t params_bytes, int math_mo
             a.h_half = (float)(0.5 * p->dt); a.h_full = (float)p->dt; a.h_sixth = (float)(p->dt / 6.0);
             a.t1 = (float)p->t1; a.rtol = (float)p->rtol; a.atol = (float)p->atol; a.dt0 = (float)p->dt0;
             a.safety = (float)p->safety; a.factor_min = (float)p->factor_min; a.factor_max = (float)p->factor_max;
-            if (p->method == PD_ODE_BS32) {
+            if (p->method != PD_ODE_RK4) {
                 a.coeff1 = (float)((p->icoeff + p->pcoeff) / (double)p->error_order);
                 a.coeff2 = (float)(-p->pcoeff / (double)p->error_order);
                 a.cursor = (unsigned long long*)scratch;

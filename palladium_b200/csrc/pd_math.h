@@ -482,4 +482,48 @@ PD_HD void pd_ctrl_powers(float err, float c1, float c2, float* r1, float* r2) {
     *r2 = pd_powf(inv, c2);
 }
 
+// ---------------------------------------------------------------------------
+// Embedded explicit Runge-Kutta pairs of order 5(4) with seven stages, the last of which is the
+// slope at the new point (first-same-as-last).  Row s of A (s = 1..6) holds the s coefficients of
+// stage s + 1; row 6 is the fifth-order weight vector.  E holds the weights of the error estimate,
+// err = h * sum_j E[j] k_j (fifth-order minus fourth-order solution).  Every coefficient is the
+// float nearest to the double expression written here, on the GPU and in the CPU oracle alike.
+//   Dormand and Prince (1980), "A family of embedded Runge-Kutta formulae", J. Comp. Appl. Math. 6.
+//   Tsitouras (2011), "Runge-Kutta pairs of order 5(4) satisfying only the first column
+//   simplifying assumption", Comput. Math. Appl. 62 -- the pair the reference's CPU comparison
+//   runs (benchmarks/bench_ensembles.py: diffrax.Tsit5).
+// ---------------------------------------------------------------------------
+#define PD_ERK_STAGES 7
+#define PD_RKF(x) ((float)(x))
+
+#define PD_DOPRI5_C {PD_RKF(0.0), PD_RKF(1.0 / 5.0), PD_RKF(3.0 / 10.0), PD_RKF(4.0 / 5.0), PD_RKF(8.0 / 9.0), \
+                     PD_RKF(1.0), PD_RKF(1.0)}
+#define PD_DOPRI5_A {                                                                                            \
+    {PD_RKF(1.0 / 5.0), 0, 0, 0, 0, 0},                                                                          \
+    {PD_RKF(3.0 / 40.0), PD_RKF(9.0 / 40.0), 0, 0, 0, 0},                                                        \
+    {PD_RKF(44.0 / 45.0), PD_RKF(-56.0 / 15.0), PD_RKF(32.0 / 9.0), 0, 0, 0},                                    \
+    {PD_RKF(19372.0 / 6561.0), PD_RKF(-25360.0 / 2187.0), PD_RKF(64448.0 / 6561.0), PD_RKF(-212.0 / 729.0), 0, 0}, \
+    {PD_RKF(9017.0 / 3168.0), PD_RKF(-355.0 / 33.0), PD_RKF(46732.0 / 5247.0), PD_RKF(49.0 / 176.0),             \
+     PD_RKF(-5103.0 / 18656.0), 0},                                                                              \
+    {PD_RKF(35.0 / 384.0), 0, PD_RKF(500.0 / 1113.0), PD_RKF(125.0 / 192.0), PD_RKF(-2187.0 / 6784.0),           \
+     PD_RKF(11.0 / 84.0)}}
+#define PD_DOPRI5_E {PD_RKF(71.0 / 57600.0), 0, PD_RKF(-71.0 / 16695.0), PD_RKF(71.0 / 1920.0),                  \
+                     PD_RKF(-17253.0 / 339200.0), PD_RKF(22.0 / 525.0), PD_RKF(-1.0 / 40.0)}
+
+#define PD_TSIT5_C {PD_RKF(0.0), PD_RKF(0.161), PD_RKF(0.327), PD_RKF(0.9), PD_RKF(0.9800255409045097),          \
+                    PD_RKF(1.0), PD_RKF(1.0)}
+#define PD_TSIT5_A {                                                                                             \
+    {PD_RKF(0.161), 0, 0, 0, 0, 0},                                                                              \
+    {PD_RKF(-0.008480655492356989), PD_RKF(0.335480655492357), 0, 0, 0, 0},                                      \
+    {PD_RKF(2.8971530571054935), PD_RKF(-6.359448489975075), PD_RKF(4.3622954328695815), 0, 0, 0},               \
+    {PD_RKF(5.325864828439257), PD_RKF(-11.748883564062828), PD_RKF(7.4955393428898365),                         \
+     PD_RKF(-0.09249506636175525), 0, 0},                                                                        \
+    {PD_RKF(5.86145544294642), PD_RKF(-12.92096931784711), PD_RKF(8.159367898576159),                            \
+     PD_RKF(-0.071584973281401), PD_RKF(-0.028269050394068383), 0},                                              \
+    {PD_RKF(0.09646076681806523), PD_RKF(0.01), PD_RKF(0.4798896504144996), PD_RKF(1.379008574103742),           \
+     PD_RKF(-3.290069515436081), PD_RKF(2.324710524099774)}}
+#define PD_TSIT5_E {PD_RKF(-0.00178001105222577714), PD_RKF(-0.0008164344596567469),                             \
+                    PD_RKF(0.007880878010261995), PD_RKF(-0.1447110071732629), PD_RKF(0.5823571654525552),       \
+                    PD_RKF(-0.45808210592918697), PD_RKF(1.0 / 66.0)}
+
 #endif  // PD_MATH_H_

@@ -132,10 +132,13 @@ def vdp_bs32(t1: float = 10.0, rtol: float = 1e-5, atol: float = 1e-7, dt0: floa
 _CHECKED_SOURCES: set = set()
 
 
+_ODE_METHODS = {"rk4": 0, "bs32": 1, "dopri5": 2, "tsit5": 3}
+
+
 def custom_ode(rhs: str, dim: int, nparam: int = 0, *, method: str = "rk4", dt: float = 0.01, steps: int = 500,
                t1: float = 10.0, rtol: float = 1e-5, atol: float = 1e-7, dt0: float = 0.01, max_steps: int = 6000,
                pcoeff: float = 0.4, icoeff: float = 0.3, safety: float = 0.9, factor_min: float = 0.2,
-               factor_max: float = 10.0, error_order: int = 3, check: bool = True,
+               factor_max: float = 10.0, error_order: int | None = None, check: bool = True,
                pallas_fn: Callable | None = None) -> Family:
     """An ensemble of independent systems y' = f(t, y, p) with a right-hand side
     of the caller's: the open end of the family set, where the reference lets a
@@ -156,11 +159,17 @@ def custom_ode(rhs: str, dim: int, nparam: int = 0, *, method: str = "rk4", dt: 
     method="bs32": adaptive Bogacki-Shampine 3(2) with the controller, counters
     and stall semantics of `vdp_bs32`; outputs t, the `dim` states, steps,
     rejected, real.
+    method="dopri5" / "tsit5": the seven-stage 5(4) pairs of Dormand-Prince and of
+    Tsitouras (what the reference's CPU comparison integrates with,
+    benchmarks/bench_ensembles.py:88-118) under the same controller and with the
+    same outputs.  `error_order` defaults to 3 for bs32 and 5 for these.
 
     With `check` (default) the source is compiled once here, without a GPU, so a
     faulty right-hand side raises EmitError where it is defined."""
-    if method not in ("rk4", "bs32"):
-        raise TraceError(f"custom_ode: method must be 'rk4' or 'bs32', got {method!r}")
+    if method not in _ODE_METHODS:
+        raise TraceError(f"custom_ode: method must be one of {sorted(_ODE_METHODS)}, got {method!r}")
+    if error_order is None:
+        error_order = 5 if method in ("dopri5", "tsit5") else 3
     if not isinstance(rhs, str) or not rhs.strip():
         raise TraceError("custom_ode: rhs must be a non-empty string of CUDA C statements")
     if not 1 <= int(dim) <= 8:
@@ -180,7 +189,7 @@ def custom_ode(rhs: str, dim: int, nparam: int = 0, *, method: str = "rk4", dt: 
 
 
 def _custom_ode_params(c: dict) -> "_native.CustomOdeParams":
-    return _native.CustomOdeParams(c["rhs"].encode(), c["dim"], c["nparam"], 0 if c["method"] == "rk4" else 1,
+    return _native.CustomOdeParams(c["rhs"].encode(), c["dim"], c["nparam"], _ODE_METHODS[c["method"]],
                                    c["dt"], c["steps"], c["t1"], c["rtol"], c["atol"], c["dt0"], c["pcoeff"],
                                    c["icoeff"], c["safety"], c["factor_min"], c["factor_max"], c["error_order"],
                                    c["max_steps"])

@@ -52,8 +52,10 @@ def test_struct_layouts_match_the_header():
 
 def test_explain_without_gpu_reports_geometry():
     info = _native.explain(0, _native.LvRk4Params(0.01, 1000), 2, (100_000,), None)
-    assert info.kernel_name.decode() == "pd_lv_rk4_kernel<1>"
-    assert info.cuda_grid[0] * info.cuda_block[0] >= 100_000
+    assert info.kernel_name.decode() == "pd_lv_rk4_kernel<2>"     # two trajectories per thread from 512 per SM up
+    assert info.cuda_grid[0] * info.cuda_block[0] * 2 >= 100_000
+    small = _native.explain(0, _native.LvRk4Params(0.01, 1000), 2, (10_000,), None)
+    assert small.kernel_name.decode() == "pd_lv_rk4_kernel<1>"
     assert info.launches == 1 and info.scratch_bytes == 0
     if _native.device_count() == 0:
         assert info.regs_per_thread == -1 and info.blocks_per_sm == -1

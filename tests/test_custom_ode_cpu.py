@@ -111,3 +111,64 @@ def test_debug_msl_shows_the_text_handed_to_the_compiler():
     src = families.source_kernel(SAXPY, "saxpy")
     args = (np.ones(1, np.float32), np.zeros(n, np.float32), np.zeros(n, np.float32))
     assert SAXPY in pd.debug_msl(src, *args, grid=(n,), out_shape=sh)
+
+
+# ------------------------------------------------------------------ the seven-stage 5(4) pairs
+def _order_condition_residuals(A, b, c, order):
+    """Largest residual of the rooted-tree order conditions up to `order` (at most 5), row sums included."""
+    one = np.ones_like(c)
+    Ac = A @ c
+    r = [np.abs(A @ one - c).max(), b @ one - 1, b @ c - 1 / 2, b @ c**2 - 1 / 3, b @ Ac - 1 / 6, b @ c**3 - 1 / 4,
+         b @ (c * Ac) - 1 / 8, b @ (A @ c**2) - 1 / 12, b @ (A @ Ac) - 1 / 24]
+    if order >= 5:
+        r += [b @ c**4 - 1 / 5, b @ (c**2 * Ac) - 1 / 10, b @ (c * (A @ c**2)) - 1 / 15, b @ (c * (A @ Ac)) - 1 / 30,
+              b @ (Ac * Ac) - 1 / 20, b @ (A @ c**3) - 1 / 20, b @ (A @ (c * Ac)) - 1 / 40,
+              b @ (A @ (A @ c**2)) - 1 / 60, b @ (A @ (A @ Ac)) - 1 / 120]
+    return max(abs(float(v)) for v in r)
+
+
+@pytest.mark.parametrize("method", ["dopri5", "tsit5"])
+def test_tableau_meets_the_order_conditions(method):
+    """The published coefficients are typed in, not derived: the 17 conditions for order five on the
+    weights, the 8 for order four on weights minus error weights, and the row sums, on the values the
+    compiled code holds (float32, hence the 1e-6), catch a wrong digit."""
+    A, c, e = oracle_custom.tableau(method)
+    b = A[6]
+    assert _order_condition_residuals(A, b, c, 5) < 1.5e-6
+    assert _order_condition_residuals(A, b - e, c, 4) < 1.5e-6
+    assert _order_condition_residuals(A, b - e, c, 5) > 1e-4      # the embedded solution is of order four only
+    assert c[5] == 1.0 and c[6] == 1.0                            # the last stage is the slope at the new point
+
+
+def test_adaptive_pairs_against_a_float64_solution():
+    """Van der Pol to t = 2 against scipy's DOP853 at rtol 1e-12: the error follows the tolerance and
+    the 5(4) pairs need a fraction of the Bogacki-Shampine steps (measured at rtol 1e-6: 34 against 243)."""
+    from scipy.integrate import solve_ivp
+
+    n = 24
+    x0, v0, mu = W.van_der_pol_ensemble(n)
+    truth = np.array([solve_ivp(lambda t, y, m=float(mu[i]): [y[1], m * (1 - y[0] ** 2) * y[1] - y[0]], (0, 2.0),
+                                [float(x0[i]), float(v0[i])], method="DOP853", rtol=1e-12, atol=1e-14).y[:, -1]
+                      for i in range(n)])
+    for rtol in (1e-4, 1e-5, 1e-6):
+        cfg = dict(t1=2.0, rtol=rtol, atol=rtol * 1e-2, dt0=0.01, max_steps=3000)
+        low = oracle_custom.bs32(VDP, 2, 1, (x0, v0, mu), **cfg)
+        for method in ("dopri5", "tsit5"):
+            out = oracle_custom.erk(VDP, 2, 1, (x0, v0, mu), method=method, **cfg)
+            assert np.all(out[0] == 2.0)
+            err = max(np.abs(out[1] - truth[:, 0]).max(), np.abs(out[2] - truth[:, 1]).max())
+            assert err < 5 * rtol, (method, rtol, err)
+            assert out[5].mean() < 0.5 * low[5].mean()
+            np.testing.assert_array_equal(out[3] + out[4], 3000.0)
+
+
+def test_adaptive_pairs_trace_like_the_other_adaptive_method():
+    n = 64
+    sh = pl.ShapeDtypeStruct((n,), np.float32)
+    for method in ("dopri5", "tsit5"):
+        fam = families.custom_ode(VDP, 2, 1, method=method)
+        assert fam.constants["error_order"] == 5
+        spec = families.trace(fam, dict(grid=(n,), out_shape=(sh,) * 6))
+        assert len(spec.inputs) == 3 and len(spec.outputs) == 6
+    assert families.custom_ode(VDP, 2, 1, method="bs32").constants["error_order"] == 3
+    assert families.custom_ode(VDP, 2, 1, method="tsit5", error_order=4).constants["error_order"] == 4

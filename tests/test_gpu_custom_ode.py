@@ -167,3 +167,50 @@ def test_concurrent_first_calls_compile_once_and_agree():
     for got in results:
         for g, w in zip(got, want):
             np.testing.assert_array_equal(g, w)
+
+
+# ------------------------------------------------------------------ the seven-stage 5(4) pairs
+@pytest.mark.parametrize("method", ["dopri5", "tsit5"])
+def test_adaptive_5_4_pairs_equal_the_oracle_bit_for_bit(method):
+    n = 3000
+    x0, v0, mu = W.van_der_pol_ensemble(n)
+    cfg = dict(t1=2.0, rtol=1e-6, atol=1e-8, dt0=0.01, max_steps=2000)
+    got = H.custom_solver(n, VDP, 2, 1, method=method, **cfg)(x0, v0, mu)
+    want = oracle_custom.erk(VDP, 2, 1, (x0, v0, mu), method=method, pow="pd", **cfg)
+    assert len(got) == 6
+    for g, w, name in zip(got, want, ("t", "x", "v", "steps", "rejected", "real")):
+        np.testing.assert_array_equal(g, w, err_msg=name)
+    assert np.all(got[0] == 2.0) and np.std(got[5]) > 0
+    ins = lorenz_ensemble(2000)
+    cfg = dict(t1=1.0, rtol=1e-5, atol=1e-7, dt0=0.001, max_steps=2000)
+    got = H.custom_solver(2000, LORENZ, 3, 3, method=method, **cfg)(*ins)
+    want = oracle_custom.erk(LORENZ, 3, 3, ins, method=method, pow="pd", **cfg)
+    assert len(got) == 7
+    for g, w in zip(got, want):
+        np.testing.assert_array_equal(g, w)
+
+
+@pytest.mark.parametrize("mode", [RELAXED, FAST])
+@pytest.mark.parametrize("method", ["dopri5", "tsit5"])
+def test_adaptive_5_4_pairs_relaxed_and_fast(method, mode):
+    """The bar the reference sets for its adaptive kernel (tests/test_08_adaptive.py:181-189):
+    state within rtol 1e-3, counters within 20."""
+    n = 3000
+    x0, v0, mu = W.van_der_pol_ensemble(n)
+    cfg = dict(t1=2.0, rtol=1e-6, atol=1e-8, dt0=0.01, max_steps=2000)
+    got = H.custom_solver(n, VDP, 2, 1, method=method, math_mode=mode, **cfg)(x0, v0, mu)
+    want = oracle_custom.erk(VDP, 2, 1, (x0, v0, mu), method=method, pow="pd", **cfg)
+    np.testing.assert_array_equal(got[0], want[0])
+    np.testing.assert_allclose(got[1], want[1], rtol=1e-3, atol=1e-5)
+    np.testing.assert_allclose(got[2], want[2], rtol=1e-3, atol=1e-5)
+    assert np.abs(got[4] - want[4]).max() <= 20 and np.abs(got[5] - want[5]).max() <= 20
+
+
+def test_a_5_4_pair_takes_fewer_attempts_than_bogacki_shampine():
+    n = 3000
+    x0, v0, mu = W.van_der_pol_ensemble(n)
+    cfg = dict(t1=2.0, rtol=1e-6, atol=1e-8, dt0=0.01, max_steps=3000)
+    low = H.custom_solver(n, VDP, 2, 1, method="bs32", **cfg)(x0, v0, mu)
+    high = H.custom_solver(n, VDP, 2, 1, method="tsit5", **cfg)(x0, v0, mu)
+    assert high[5].mean() < 0.3 * low[5].mean()
+    np.testing.assert_allclose(high[1], low[1], rtol=2e-4, atol=2e-5)
