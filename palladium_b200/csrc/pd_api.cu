@@ -1007,7 +1007,7 @@ thread_local HostStaging t_staging;
 }  // namespace
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point table (no link against libcuda).
-cudaError_t pd_encode_field_map(CUtensorMap* map, const float* base, int rows, int cols, int box_rows) {
+cudaError_t pd_encode_field_map(CUtensorMap* map, const float* base, int rows, int cols, int box_rows, int box_cols) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1025,7 +1025,7 @@ cudaError_t pd_encode_field_map(CUtensorMap* map, const float* base, int rows, i
     if (!encode) return cudaErrorNotSupported;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};   // bytes between rows; a multiple of 16
-    const cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1u, 1u};
     const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,

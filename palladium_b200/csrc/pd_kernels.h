@@ -153,8 +153,8 @@ inline void pd_gs_set_constants(PdGsArgs& a, double du, double dv, double f, dou
     a.du = (float)du; a.dv = (float)dv; a.f = (float)f; a.fk = (float)(f + k); a.dt = (float)dt;
 }
 
-// A 2-D tensor map over one row-major float32 field of this GPU (rows x cols), box = box_rows x 128
-// columns, out-of-range elements read as zero.  Implemented once, in the C-ABI translation unit.
-cudaError_t pd_encode_field_map(CUtensorMap* map, const float* base, int rows, int cols, int box_rows);
+// A 2-D tensor map over one row-major float32 field of this GPU (rows x cols), box = box_rows x box_cols,
+// out-of-range elements read as zero.  Implemented once, in the C-ABI translation unit.
+cudaError_t pd_encode_field_map(CUtensorMap* map, const float* base, int rows, int cols, int box_rows, int box_cols);
 
 #endif  // PD_KERNELS_H_
