@@ -214,3 +214,46 @@ def test_a_5_4_pair_takes_fewer_attempts_than_bogacki_shampine():
     high = H.custom_solver(n, VDP, 2, 1, method="tsit5", **cfg)(x0, v0, mu)
     assert high[5].mean() < 0.3 * low[5].mean()
     np.testing.assert_allclose(high[1], low[1], rtol=2e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize("method", ["dopri5", "tsit5"])
+def test_adaptive_5_4_pairs_edge_cases_follow_the_oracle(method):
+    """Non-finite and degenerate lanes (a NaN state rejects every attempt, an overflowing parameter,
+    the fixed point whose error estimate is exactly zero), a budget far too small, and a zero budget."""
+    n = 96
+    x0, v0, mu = (a.copy() for a in W.van_der_pol_ensemble(n))
+    x0[0] = np.nan
+    mu[1] = 1e30
+    v0[2] = np.inf
+    x0[3], v0[3] = 0.0, 0.0
+    mu[4] = 0.0
+    cfg = dict(t1=2.0, rtol=1e-5, atol=1e-7, dt0=1e-2, max_steps=400)
+    got = H.custom_solver(n, VDP, 2, 1, method=method, **cfg)(x0, v0, mu)
+    want = oracle_custom.erk(VDP, 2, 1, (x0, v0, mu), method=method, pow="pd", **cfg)
+    for g, w, name in zip(got, want, ("t", "x", "v", "steps", "rejected", "real")):
+        np.testing.assert_array_equal(g, w, err_msg=name)
+    assert got[4][0] == cfg["max_steps"] and got[0][3] == np.float32(cfg["t1"])
+
+    x0, v0, mu = W.van_der_pol_ensemble(257)
+    cfg = dict(t1=20.0, rtol=1e-6, atol=1e-8, dt0=1e-3, max_steps=40)
+    got = H.custom_solver(257, VDP, 2, 1, method=method, **cfg)(x0, v0, mu)
+    want = oracle_custom.erk(VDP, 2, 1, (x0, v0, mu), method=method, pow="pd", **cfg)
+    for g, w in zip(got, want):
+        np.testing.assert_array_equal(g, w)
+    assert (got[0] < 20.0).any() and (got[3] + got[4] == 40).all()
+
+    t, x, v, steps, rejected, real = H.custom_solver(257, VDP, 2, 1, method=method, max_steps=0)(x0, v0, mu)
+    np.testing.assert_array_equal(x, x0)
+    assert (t == 0).all() and (steps == 0).all() and (real == 0).all()
+
+
+def test_adaptive_5_4_pair_scalar_system_without_parameters():
+    n = 1000
+    y0 = np.linspace(0.1, 2.0, n).astype(np.float32)
+    cfg = dict(t1=1.0, rtol=1e-6, atol=1e-9, dt0=1e-2, max_steps=300)
+    got = H.custom_solver(n, "dy[0] = -y[0] * y[0];", 1, 0, method="tsit5", **cfg)(y0)
+    want = oracle_custom.erk("dy[0] = -y[0] * y[0];", 1, 0, (y0,), method="tsit5", pow="pd", **cfg)
+    assert len(got) == 5
+    for g, w in zip(got, want):
+        np.testing.assert_array_equal(g, w)
+    np.testing.assert_allclose(got[1], y0 / (1.0 + y0), rtol=5e-6)    # y' = -y^2: y(1) = y0 / (1 + y0)
