@@ -96,12 +96,61 @@ PD_HD float pd_div_nonneg(float a, float b) {
     q = __fmaf_rn(__fmaf_rn(-b, q, as), y, q);
     return small ? __fmul_rn(q, 5.42101086242752217e-20f) : q;
 }
+// Two such quotients at once: the Newton and residual steps, all fused multiply-adds, on packed
+// f32x2 instructions (each half rounds as the scalar sequence does); operands outside the fast
+// range send both quotients down the scalar function.
+PD_HD void pd_div_nonneg_pair(float a1, float b1, float a2, float b2, float* q1, float* q2) {
+    const uint32_t ia1 = __float_as_uint(a1), ib1 = __float_as_uint(b1);
+    const uint32_t ia2 = __float_as_uint(a2), ib2 = __float_as_uint(b2);
+    const bool ok = (ib1 - 0x21800000u) < 0x28000000u && (ib2 - 0x21800000u) < 0x28000000u &&
+                    (ia1 == 0u || (ia1 - 0x0B800000u) < 0x52000000u) &&
+                    (ia2 == 0u || (ia2 - 0x0B800000u) < 0x52000000u);
+    if (!ok) {
+        *q1 = pd_div_nonneg(a1, b1);
+        *q2 = pd_div_nonneg(a2, b2);
+        return;
+    }
+    const bool small1 = ia1 < 0x21800000u, small2 = ia2 < 0x21800000u;
+    const float2 as = make_float2(small1 ? __fmul_rn(a1, 18446744073709551616.0f) : a1,
+                                  small2 ? __fmul_rn(a2, 18446744073709551616.0f) : a2);
+    const float2 nb = make_float2(-b1, -b2), one = make_float2(1.0f, 1.0f);
+    float y1, y2;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y1) : "f"(b1));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y2) : "f"(b2));
+    float2 y = make_float2(y1, y2);
+    y = __ffma2_rn(y, __ffma2_rn(nb, y, one), y);
+    float2 q = __fmul2_rn(as, y);          // consumed by fused multiply-adds only
+    q = __ffma2_rn(__ffma2_rn(nb, q, as), y, q);
+    q = __ffma2_rn(__ffma2_rn(nb, q, as), y, q);
+    *q1 = small1 ? __fmul_rn(q.x, 5.42101086242752217e-20f) : q.x;
+    *q2 = small2 ? __fmul_rn(q.y, 5.42101086242752217e-20f) : q.y;
+}
 #else
 PD_HD float pd_div_nonneg(float a, float b) { return a / b; }
+PD_HD void pd_div_nonneg_pair(float a1, float b1, float a2, float b2, float* q1, float* q2) {
+    *q1 = a1 / b1;
+    *q2 = a2 / b2;
+}
 #endif
 
 // NaN-propagating min / max: the semantics of the staged `max` / `min`
 // primitives the reference kernels use (jnp.maximum / jnp.minimum).
+// On the device they are single instructions (max.NaN / min.NaN): a NaN operand gives the canonical
+// NaN where the host form hands on the operand's own NaN, which no comparison of values can tell
+// apart; for a +0 / -0 pair the instruction orders -0 below +0 and the host form returns its second
+// operand, a case the callers never produce (they compare non-negative quantities).
+#if defined(__CUDA_ARCH__)
+PD_HD float pd_max_nan(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+PD_HD float pd_min_nan(float a, float b) {
+    float r;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+#else
 PD_HD float pd_max_nan(float a, float b) {
     if (a != a) return a;
     if (b != b) return b;
@@ -112,6 +161,7 @@ PD_HD float pd_min_nan(float a, float b) {
     if (b != b) return b;
     return a < b ? a : b;
 }
+#endif
 
 // ---------------------------------------------------------------------------
 // Threefry-2x32-20.
@@ -452,15 +502,21 @@ PD_HD float pd_ctrl_log2(float x) {   // x: positive, normal, finite
     return pd_fma(t, q, (float)e);
 }
 
+#define PD_EXP2_C6 1.546973217e-04f
+#define PD_EXP2_C5 1.339086681e-03f
+#define PD_EXP2_C4 9.618030861e-03f
+#define PD_EXP2_C3 5.550356954e-02f
+#define PD_EXP2_C2 2.402265072e-01f
+#define PD_EXP2_C1 6.931471825e-01f
 PD_HD float pd_ctrl_exp2(float w) {   // |w| <= 120
     const float nf = floorf(pd_add(w, 0.5f));
     const float f = pd_sub(w, nf);                        // exact, |f| <= 1/2
-    float p = 1.546973217e-04f;
-    p = pd_fma(p, f, 1.339086681e-03f);
-    p = pd_fma(p, f, 9.618030861e-03f);
-    p = pd_fma(p, f, 5.550356954e-02f);
-    p = pd_fma(p, f, 2.402265072e-01f);
-    p = pd_fma(p, f, 6.931471825e-01f);
+    float p = PD_EXP2_C6;
+    p = pd_fma(p, f, PD_EXP2_C5);
+    p = pd_fma(p, f, PD_EXP2_C4);
+    p = pd_fma(p, f, PD_EXP2_C3);
+    p = pd_fma(p, f, PD_EXP2_C2);
+    p = pd_fma(p, f, PD_EXP2_C1);
     const float r = pd_fma(p, f, 1.0f);                   // 2**0 is exactly 1
     return pd_mul(r, pd_u2f((uint32_t)((int)nf + 127) << 23));
 }
@@ -472,8 +528,30 @@ PD_HD void pd_ctrl_powers(float err, float c1, float c2, float* r1, float* r2) {
         const float l = -pd_ctrl_log2(err);               // log2(1 / err)
         const float w1 = pd_mul(c1, l), w2 = pd_mul(c2, l);
         if (fabsf(w1) <= 120.0f && fabsf(w2) <= 120.0f) {
+#if defined(__CUDA_ARCH__)
+            // pd_ctrl_exp2 for both arguments at once on packed f32x2 instructions: each half goes
+            // through the operations of the scalar function with the same roundings (w - nf as the
+            // exact fma nf * (-1) + w; no packed multiply here has an add as its only consumer, which
+            // is the one pattern the assembler would fuse).
+            const float2 w = make_float2(w1, w2);
+            const float2 nf = make_float2(floorf(pd_add(w1, 0.5f)), floorf(pd_add(w2, 0.5f)));
+            const float2 f = __ffma2_rn(nf, make_float2(-1.0f, -1.0f), w);
+            float2 q = make_float2(PD_EXP2_C6, PD_EXP2_C6);
+            q = __ffma2_rn(q, f, make_float2(PD_EXP2_C5, PD_EXP2_C5));
+            q = __ffma2_rn(q, f, make_float2(PD_EXP2_C4, PD_EXP2_C4));
+            q = __ffma2_rn(q, f, make_float2(PD_EXP2_C3, PD_EXP2_C3));
+            q = __ffma2_rn(q, f, make_float2(PD_EXP2_C2, PD_EXP2_C2));
+            q = __ffma2_rn(q, f, make_float2(PD_EXP2_C1, PD_EXP2_C1));
+            q = __ffma2_rn(q, f, make_float2(1.0f, 1.0f));
+            const float2 scale = make_float2(pd_u2f((uint32_t)((int)nf.x + 127) << 23),
+                                             pd_u2f((uint32_t)((int)nf.y + 127) << 23));
+            const float2 r = __fmul2_rn(q, scale);
+            *r1 = r.x;
+            *r2 = r.y;
+#else
             *r1 = pd_ctrl_exp2(w1);
             *r2 = pd_ctrl_exp2(w2);
+#endif
             return;
         }
     }

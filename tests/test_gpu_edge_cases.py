@@ -150,6 +150,12 @@ extern "C" __global__ void div_check(const uint32_t* key, const uint32_t* range,
         const float a = pd_u2f(((a_lo + (ra >> 23) % a_n) << 23) | ma);
         const float b = pd_u2f(((b_lo + (rb >> 23) % b_n) << 23) | mb);
         count += pd_f2u(pd_div_nonneg(a, b)) != pd_f2u(__fdiv_rn(a, b)) ? 1u : 0u;
+        // the two-quotient form (packed instructions), this pair next to the swapped-significand one
+        const float a2 = pd_u2f(((a_lo + (rb >> 23) % a_n) << 23) | mb), b2 = pd_u2f(((b_lo + (ra >> 23) % b_n) << 23) | ma);
+        float q1, q2;
+        pd_div_nonneg_pair(a, b, a2, b2, &q1, &q2);
+        count += pd_f2u(q1) != pd_f2u(__fdiv_rn(a, b)) ? 1u : 0u;
+        count += pd_f2u(q2) != pd_f2u(__fdiv_rn(a2, b2)) ? 1u : 0u;
     }
     // the special values, once per thread: zero numerators, and operands outside the stated range
     const float special[8] = {0.0f, 1e-42f, 3e38f, 1.0f, pd_u2f(0x7F800000u), pd_u2f(0x7FC00000u), -1.0f, 1e-30f};
@@ -158,6 +164,11 @@ extern "C" __global__ void div_check(const uint32_t* key, const uint32_t* range,
             const uint32_t want = pd_f2u(__fdiv_rn(special[p], special[q])), got = pd_f2u(pd_div_nonneg(special[p], special[q]));
             const bool both_nan = (want & 0x7FFFFFFFu) > 0x7F800000u && (got & 0x7FFFFFFFu) > 0x7F800000u;
             count += (want != got && !both_nan) ? 1u : 0u;
+            float q1, q2;   // a special value beside an ordinary quotient sends both down the scalar path
+            pd_div_nonneg_pair(special[p], special[q], 3.0f, 7.0f, &q1, &q2);
+            const bool nan1 = (want & 0x7FFFFFFFu) > 0x7F800000u && (pd_f2u(q1) & 0x7FFFFFFFu) > 0x7F800000u;
+            count += (want != pd_f2u(q1) && !nan1) ? 1u : 0u;
+            count += pd_f2u(q2) != pd_f2u(__fdiv_rn(3.0f, 7.0f)) ? 1u : 0u;
         }
     bad[i] = count;
 }
@@ -177,3 +188,35 @@ def test_safe_division_equals_ieee_division_bit_for_bit(name, a_lo, a_n, b_lo, b
                         out_shape=pl.ShapeDtypeStruct((threads,), np.uint32), math_mode=SAFE)
     bad = call(W.gbm_key(11), np.array([a_lo, a_n, b_lo, b_n, reps], np.uint32))
     assert int(bad.sum()) == 0, f"{int(bad.sum())} of {threads * reps} quotients differ: {name}"
+
+
+CTRL_POW = r'''
+extern "C" __global__ void ctrl_pow(const float* err, const float* c, float* r1, float* r2,
+                                    long long gx, long long gy, long long gz) {
+    const long long i = PD_THREAD_X;
+    if (i >= gx) return;
+    pd_ctrl_powers(err[i], c[0], c[1], &r1[i], &r2[i]);
+}
+'''
+
+
+def test_controller_powers_on_the_device_equal_the_host_routine_bit_for_bit():
+    """The device evaluates the controller's two powers on packed instructions, the CPU oracle one
+    after the other: every bit must agree, the integer step counts depend on it.  Two million error
+    norms over the range the controller sees and beyond it, the special values included."""
+    from palladium_b200 import families, pl
+
+    rng = np.random.default_rng(8)
+    err = np.concatenate([np.exp(rng.uniform(np.log(1e-9), np.log(1e9), 1 << 21)).astype(np.float32),
+                          np.exp(rng.uniform(np.log(1e-38), np.log(1e38), 1 << 18)).astype(np.float32),
+                          np.array([0.0, np.inf, np.nan, 1e-42, 1.0, 1e-9, -1.0], np.float32)])
+    n = err.size
+    sh = pl.ShapeDtypeStruct((n,), np.float32)
+    call = pd.cuda_call(families.source_kernel(CTRL_POW, "ctrl_pow"), grid=(n,), out_shape=(sh, sh), math_mode=SAFE)
+    for c1, c2 in ((0.7 / 3, -0.4 / 3), (0.7 / 5, -0.4 / 5), (0.5, -0.25), (20.0, -20.0)):
+        coeff = np.array([c1, c2], np.float32)
+        r1, r2 = call(err, coeff)
+        np.testing.assert_array_equal(r1.view(np.uint32)[:-5], oracle.pd_ctrl_pow(err, coeff[0]).view(np.uint32)[:-5])
+        np.testing.assert_array_equal(r2.view(np.uint32)[:-5], oracle.pd_ctrl_pow(err, coeff[1]).view(np.uint32)[:-5])
+        np.testing.assert_array_equal(r1, oracle.pd_ctrl_pow(err, coeff[0]))      # NaN where the host has NaN
+        np.testing.assert_array_equal(r2, oracle.pd_ctrl_pow(err, coeff[1]))
