@@ -265,6 +265,69 @@ def bench_custom_ode(n: int, steps: int, math_mode: str = "fast", rhs: str = CUS
     return res
 
 
+def fixed_costs(calls: int = 300) -> dict:
+    """The per-call costs the reference documents for its runtime (docs/performance.md:35-48: a
+    blocking dispatch floor of about 136 us, about 33 us per dispatch at in-flight depth 16, about
+    0.25 ms of jit-path overhead at 16 KB and 1 MB buffers), measured the same way here: a kernel
+    too small to matter (Lotka-Volterra, one RK4 step), medians of `calls` wall-clock samples."""
+    import torch
+
+    from palladium_b200 import cuda_call, cuda_call_jit, families, pl
+
+    spec_1 = pl.BlockSpec((1,), lambda i: (i,))
+
+    def make(n, jit):
+        fam = families.lv_rk4(0.01, 1)
+        if jit:
+            return cuda_call_jit(fam, grid=(n,), out_shape=(_shaped((n,)), _shaped((n,))), math_mode="fast")
+        return cuda_call(fam, grid=(n,), in_specs=[spec_1] * 6, out_specs=(spec_1, spec_1),
+                         out_shape=(_shaped((n,)), _shaped((n,))), math_mode="fast")
+
+    def median_us(fn, per=1):
+        fn()
+        samples = []
+        for _ in range(calls):
+            t0 = time.perf_counter()
+            fn()
+            samples.append((time.perf_counter() - t0) / per)
+        return float(np.median(samples)) * 1e6
+
+    out = {}
+    for label, n in (("16KB", 4096), ("1MB", 262144)):
+        arrays = [np.full(n, 1.0, np.float32) for _ in range(6)]
+        eager, jit = make(n, False), make(n, True)
+        dev = [torch.from_numpy(a).cuda() for a in arrays]
+        outs = [torch.empty(n, device="cuda") for _ in range(2)]
+        out[f"eager_blocking_call_us_{label}"] = median_us(lambda: eager(*arrays))
+        out[f"jit_host_arrays_call_us_{label}"] = median_us(lambda: jit(*arrays))
+        pinned = eager.pin(*arrays)
+        out[f"pinned_inputs_call_us_{label}"] = median_us(pinned)
+
+        def burst():
+            pending = [eager.launch(*arrays) for _ in range(16)]
+            for h in pending:
+                h.wait()
+
+        out[f"launch_wait_depth16_us_per_dispatch_{label}"] = median_us(burst, per=16)
+
+        def stream_ordered():
+            for _ in range(16):
+                jit.on_device(*dev, out=outs)
+            torch.cuda.synchronize()
+
+        out[f"jit_device_tensors_us_per_call_depth16_{label}"] = median_us(stream_ordered, per=16)
+
+        def blocking_device():
+            jit(*dev)
+            torch.cuda.synchronize()
+
+        out[f"jit_device_tensors_blocking_call_us_{label}"] = median_us(blocking_device)
+    out["reference_published"] = {"blocking_dispatch_floor_us": 136, "depth16_us_per_dispatch": 33,
+                                  "jit_overhead_us_16KB": 190, "jit_overhead_us_1MB": 250,
+                                  "hardware": "Apple M1 Pro (docs/performance.md:35-44)"}
+    return out
+
+
 def quick_summary(named: bool = True) -> dict:
     """Each family once at a reduced size that finishes in a few seconds, the headline kernel under the
     other two math modes, and (named=True) every benchmark configuration at its full named size."""
@@ -282,6 +345,7 @@ def quick_summary(named: bool = True) -> dict:
     out["lv_df32"] = bench_lv_df32(1 << 20, 100, fma_peak=fma_peak)
     out["custom_ode_lv"] = bench_custom_ode(1 << 22, 1000, "fast", fma_peak=fma_peak)
     out["vdp_tsit5_safe"] = bench_vdp_pair(1 << 18, "tsit5", "safe")
+    out["fixed_costs"] = fixed_costs()
     out.update(named_rk4_modes(fma_peak))
     if named:
         out.update(named_configs(fma_peak, int_peak))

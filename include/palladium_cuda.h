@@ -310,6 +310,28 @@ PD_API int pd_dispatch_host(int family, const void* params, size_t params_bytes,
                      int n_out, void* const* out, const size_t* out_bytes,
                      char* err, size_t err_cap);
 
+/* The same call in two halves, for callers that keep several calls in flight: what
+ * BoundKernel.launch() / PendingResult.wait() are in the reference
+ * (src/palladium/dispatch.py:129-194; docs/performance.md:35-40 quotes 33 us per
+ * dispatch at depth 16 against 136 us for a blocking one).
+ * pd_submit_host copies the inputs into page-locked memory of the library -- the
+ * caller's arrays may change as soon as it returns --, queues one upload, the
+ * kernels and one download on a stream of the call's own and hands back a ticket.
+ * pd_wait_host blocks until that call has finished, copies the results into `out`
+ * (sizes as submitted) and retires the ticket; with n_out == 0 it only retires it.
+ * `out` of pd_submit_host is NULL for that form.  Alternatively it names the result
+ * arrays up front: they must be page-locked (an ordinary array would make the
+ * submission wait for the kernels) and stay alive until the wait, which is then
+ * called with n_out == 0 and copies nothing.
+ * At most 64 calls may be in flight in a process; every ticket must be waited for. */
+PD_API int pd_submit_host(int family, const void* params, size_t params_bytes, int math_mode,
+                   const int64_t grid[3], const int64_t block[3],
+                   int n_in, const void* const* in, const size_t* in_bytes,
+                   int n_out, void* const* out, const size_t* out_bytes, uint64_t* ticket,
+                   char* err, size_t err_cap);
+PD_API int pd_wait_host(uint64_t ticket, int n_out, void* const* out, const size_t* out_bytes,
+                 char* err, size_t err_cap);
+
 /* Launch geometry for a call, without launching anything (the native half of
  * MetalCallable.explain, src/palladium/__init__.py:116-128).  Works without a
  * GPU; the register / shared-memory / occupancy fields are then -1. */

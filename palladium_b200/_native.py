@@ -42,6 +42,8 @@ EXPORTED_SYMBOLS = (
     "pd_device_count",
     "pd_launch",
     "pd_dispatch_host",
+    "pd_submit_host",
+    "pd_wait_host",
     "pd_explain",
     "pd_set_tuning",
     "pd_get_tuning",
@@ -163,6 +165,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pd_launch.argtypes = [ci, vp, sz, ci, i64p, i64p, ci, vpp, szp, ci, vpp, szp, vp, sz, vp, cp, sz]
     lib.pd_dispatch_host.restype = ci
     lib.pd_dispatch_host.argtypes = [ci, vp, sz, ci, i64p, i64p, ci, vpp, szp, ci, vpp, szp, cp, sz]
+    lib.pd_submit_host.restype = ci
+    lib.pd_submit_host.argtypes = [ci, vp, sz, ci, i64p, i64p, ci, vpp, szp, ci, vpp, szp, ctypes.POINTER(ctypes.c_uint64), cp, sz]
+    lib.pd_wait_host.restype = ci
+    lib.pd_wait_host.argtypes = [ctypes.c_uint64, ci, vpp, szp, cp, sz]
     lib.pd_explain.restype = ci
     lib.pd_explain.argtypes = [ci, vp, sz, ci, i64p, i64p, ctypes.POINTER(LaunchInfo), cp, sz]
     lib.pd_set_tuning.restype = ci
@@ -286,6 +292,37 @@ def dispatch_host(family: int, params: ctypes.Structure, math_mode: int, grid, b
     err = ctypes.create_string_buffer(_ERR_CAP)
     rc = lib.pd_dispatch_host(family, ctypes.addressof(params), ctypes.sizeof(params), math_mode, garr, barr, n_in,
                               in_ptrs, in_sizes, n_out, out_ptrs, out_sizes, err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+
+
+def submit_host(family: int, params: ctypes.Structure, math_mode: int, grid, block, inputs, out_sizes,
+                out_ptrs=None) -> int:
+    """pd_submit_host: queue a call on host pointers without waiting for it; returns the ticket.
+    inputs: (pointer, bytes) pairs, copied before the call returns; out_sizes: bytes per output;
+    out_ptrs: page-locked result arrays to download into directly (else the results are collected
+    by wait_host)."""
+    lib = library()
+    garr, barr = _arrays(grid, block)
+    n_in, in_ptrs, in_sizes = _buffers(inputs)
+    n_out = len(out_sizes)
+    sizes = (ctypes.c_size_t * max(n_out, 1))(*out_sizes)
+    outs = (ctypes.c_void_p * max(n_out, 1))(*out_ptrs) if out_ptrs is not None else None
+    ticket = ctypes.c_uint64(0)
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = lib.pd_submit_host(family, ctypes.addressof(params), ctypes.sizeof(params), math_mode, garr, barr, n_in,
+                            in_ptrs, in_sizes, n_out, outs, sizes, ctypes.byref(ticket), err, _ERR_CAP)
+    if rc:
+        _raise(rc, err.value)
+    return ticket.value
+
+
+def wait_host(ticket: int, outputs) -> None:
+    """pd_wait_host: block until the call behind `ticket` has finished and copy its results into
+    `outputs` ((pointer, bytes) pairs; an empty list only retires the ticket)."""
+    n_out, out_ptrs, out_sizes = _buffers(outputs)
+    err = ctypes.create_string_buffer(_ERR_CAP)
+    rc = library().pd_wait_host(ctypes.c_uint64(ticket), n_out, out_ptrs, out_sizes, err, _ERR_CAP)
     if rc:
         _raise(rc, err.value)
 

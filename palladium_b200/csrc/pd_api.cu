@@ -1335,6 +1335,224 @@ int pd_dispatch_host(int family, const void* params, size_t params_bytes, int ma
     return rc;
 }
 
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Asynchronous host-buffer calls: pd_submit_host / pd_wait_host.
+// A slot owns one page-locked host block and one device block (inputs first, then outputs, each
+// at a 256-byte offset), a stream and an event.  Submitting packs the inputs into the host block
+// -- so the caller may change its arrays as soon as the call returns -- and queues ONE upload,
+// the kernels and ONE download on the slot's stream; waiting synchronises the event, copies the
+// results out and frees the slot for the next submission.
+// ---------------------------------------------------------------------------
+namespace {
+
+struct AsyncSlot {
+    int device = -1;
+    bool busy = false;
+    uint64_t ticket = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t done = nullptr;
+    unsigned char* host = nullptr;
+    unsigned char* dev = nullptr;
+    size_t capacity = 0;
+    size_t out_begin = 0;
+    bool direct_out = false;   // the results went straight to arrays the caller named at submission
+    std::vector<size_t> out_offset, out_bytes;
+};
+const int kMaxAsyncSlots = 64;
+std::mutex g_async_mutex;
+std::vector<AsyncSlot*>& async_slots() {
+    static std::vector<AsyncSlot*> slots;
+    return slots;
+}
+uint64_t g_next_ticket = 1;
+
+size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace
+
+extern "C" {
+
+int pd_submit_host(int family, const void* params, size_t params_bytes, int math_mode, const int64_t grid[3],
+                   const int64_t block[3], int n_in, const void* const* in, const size_t* in_bytes, int n_out,
+                   void* const* out, const size_t* out_bytes, uint64_t* ticket, char* err, size_t err_cap) {
+    DeviceFacts dev = device_facts();
+    if (!dev.present)
+        return fail(PD_ERR_CUDA, err, err_cap, "no CUDA device is available: libpalladium_cuda has no CPU fallback");
+    if (!ticket) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "ticket must not be NULL");
+    if (n_in < 0 || n_out < 0 || n_in > 64 || n_out > 64)
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "buffer count out of range");
+    if ((n_in > 0 && (!in || !in_bytes)) || (n_out > 0 && !out_bytes))
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "buffer arrays must not be NULL");
+    for (int i = 0; i < n_in; ++i)
+        if (in_bytes[i] && !in[i]) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "input %d: NULL pointer", i);
+    size_t total = 0;
+    std::vector<size_t> in_offset(n_in), out_offset(n_out);
+    for (int i = 0; i < n_in; ++i) { in_offset[i] = total; total += align256(in_bytes[i]); }
+    const size_t out_begin = total;
+    for (int i = 0; i < n_out; ++i) { out_offset[i] = total; total += align256(out_bytes[i]); }
+    if (total == 0) total = 256;
+
+    AsyncSlot* slot = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_async_mutex);
+        std::vector<AsyncSlot*>& slots = async_slots();
+        for (AsyncSlot* s : slots)   // a free slot that is large enough, else any free slot (it grows below)
+            if (!s->busy && s->device == dev.device && s->capacity >= total) { slot = s; break; }
+        if (!slot)
+            for (AsyncSlot* s : slots)
+                if (!s->busy && s->device == dev.device) { slot = s; break; }
+        if (!slot) {
+            if ((int)slots.size() >= kMaxAsyncSlots)
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                            "%d host-buffer calls are in flight: wait for earlier results before submitting more",
+                            kMaxAsyncSlots);
+            slot = new AsyncSlot();
+            slot->device = dev.device;
+            slots.push_back(slot);
+        }
+        slot->busy = true;
+        slot->ticket = g_next_ticket++;
+    }
+    auto release = [&](int rc) {
+        std::lock_guard<std::mutex> lock(g_async_mutex);
+        slot->busy = false;
+        return rc;
+    };
+    auto cuda_fail = [&](cudaError_t e, const char* what) {
+        cudaGetLastError();
+        return release(fail(PD_ERR_CUDA, err, err_cap, "%s failed: %s", what, cudaGetErrorString(e)));
+    };
+    cudaError_t e;
+    if (!slot->stream) {
+        if ((e = cudaStreamCreateWithFlags(&slot->stream, cudaStreamNonBlocking)) != cudaSuccess)
+            return cuda_fail(e, "cudaStreamCreateWithFlags");
+        if ((e = cudaEventCreateWithFlags(&slot->done, cudaEventDisableTiming)) != cudaSuccess)
+            return cuda_fail(e, "cudaEventCreateWithFlags");
+    }
+    if (slot->capacity < total) {
+        // the slot is free, so nothing of an earlier call still uses its blocks
+        if (slot->host) { cudaFreeHost(slot->host); slot->host = nullptr; }
+        if (slot->dev) { cudaFree(slot->dev); slot->dev = nullptr; }
+        slot->capacity = 0;
+        const size_t want = total < 65536 ? 65536 : total;
+        if ((e = cudaHostAlloc((void**)&slot->host, want, cudaHostAllocDefault)) != cudaSuccess)
+            return cuda_fail(e, "cudaHostAlloc");
+        if ((e = cudaMalloc((void**)&slot->dev, want)) != cudaSuccess) return cuda_fail(e, "cudaMalloc");
+        slot->capacity = want;
+    }
+    if (out_begin < ((size_t)256 << 10)) {
+        // small inputs: packed into the slot's block and uploaded by one copy
+        for (int i = 0; i < n_in; ++i)
+            if (in_bytes[i]) memcpy(slot->host + in_offset[i], in[i], in_bytes[i]);
+        if (out_begin) {
+            if ((e = cudaMemcpyAsync(slot->dev, slot->host, out_begin, cudaMemcpyHostToDevice, slot->stream)) != cudaSuccess)
+                return cuda_fail(e, "cudaMemcpyAsync (upload)");
+        }
+    } else {
+        // Large inputs: a copy from ordinary (pageable) memory returns once the driver has staged the
+        // source, so the caller's array is free again without a second pass over it on this thread;
+        // page-locked or managed sources would be read asynchronously and go through the slot's block.
+        for (int i = 0; i < n_in; ++i) {
+            if (!in_bytes[i]) continue;
+            cudaPointerAttributes attr;
+            const bool pageable = cudaPointerGetAttributes(&attr, in[i]) == cudaSuccess &&
+                                  attr.type == cudaMemoryTypeUnregistered;
+            cudaGetLastError();
+            const void* src = in[i];
+            if (!pageable) {
+                memcpy(slot->host + in_offset[i], in[i], in_bytes[i]);
+                src = slot->host + in_offset[i];
+            }
+            if ((e = cudaMemcpyAsync(slot->dev + in_offset[i], src, in_bytes[i], cudaMemcpyHostToDevice, slot->stream)) !=
+                cudaSuccess) {
+                cudaStreamSynchronize(slot->stream);
+                return cuda_fail(e, "cudaMemcpyAsync (upload)");
+            }
+        }
+    }
+    std::vector<const void*> d_in(n_in);
+    std::vector<void*> d_out(n_out);
+    for (int i = 0; i < n_in; ++i) d_in[i] = slot->dev + in_offset[i];
+    for (int i = 0; i < n_out; ++i) d_out[i] = slot->dev + out_offset[i];
+    int rc = launch_impl(family, params, params_bytes, math_mode, grid, block, n_in, d_in.data(), in_bytes, n_out,
+                         d_out.data(), out_bytes, nullptr, 0, slot->stream, err, err_cap);
+    if (rc) {
+        cudaStreamSynchronize(slot->stream);   // the upload still reads the slot's host block
+        return release(rc);
+    }
+    if (out) {
+        // the caller's own (page-locked) result arrays: one download each, nothing to copy at the wait
+        for (int i = 0; i < n_out; ++i) {
+            if (!out_bytes[i]) continue;
+            if (!out[i]) {
+                cudaStreamSynchronize(slot->stream);
+                return release(fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output %d: NULL pointer", i));
+            }
+            if ((e = cudaMemcpyAsync(out[i], slot->dev + out_offset[i], out_bytes[i], cudaMemcpyDeviceToHost,
+                                     slot->stream)) != cudaSuccess) {
+                cudaStreamSynchronize(slot->stream);
+                return cuda_fail(e, "cudaMemcpyAsync (download)");
+            }
+        }
+    } else if (total > out_begin && n_out > 0) {
+        if ((e = cudaMemcpyAsync(slot->host + out_begin, slot->dev + out_begin, total - out_begin, cudaMemcpyDeviceToHost,
+                                 slot->stream)) != cudaSuccess) {
+            cudaStreamSynchronize(slot->stream);
+            return cuda_fail(e, "cudaMemcpyAsync (download)");
+        }
+    }
+    if ((e = cudaEventRecord(slot->done, slot->stream)) != cudaSuccess) {
+        cudaStreamSynchronize(slot->stream);
+        return cuda_fail(e, "cudaEventRecord");
+    }
+    slot->out_begin = out_begin;
+    slot->out_offset = out_offset;
+    slot->out_bytes.assign(out_bytes, out_bytes + n_out);
+    slot->direct_out = out != nullptr;
+    *ticket = slot->ticket;
+    return PD_OK;
+}
+
+int pd_wait_host(uint64_t ticket, int n_out, void* const* out, const size_t* out_bytes, char* err, size_t err_cap) {
+    AsyncSlot* slot = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_async_mutex);
+        for (AsyncSlot* s : async_slots())
+            if (s->busy && s->ticket == ticket) { slot = s; break; }
+    }
+    if (!slot) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "unknown or already retired ticket");
+    auto release = [&](int rc) {
+        std::lock_guard<std::mutex> lock(g_async_mutex);
+        slot->busy = false;
+        return rc;
+    };
+    cudaError_t e = cudaEventSynchronize(slot->done);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return release(fail(PD_ERR_CUDA, err, err_cap, "cudaEventSynchronize failed: %s", cudaGetErrorString(e)));
+    }
+    int rc = check_device_status(slot->device, err, err_cap);
+    if (rc) return release(rc);
+    if (n_out != 0 && slot->direct_out)
+        return release(fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                            "the results of this call went to the arrays named at submission; wait with n_out = 0"));
+    if (n_out != 0) {   // n_out == 0 retires the ticket without collecting anything
+        if (n_out != (int)slot->out_bytes.size() || !out || !out_bytes)
+            return release(fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "the call produced %d arrays, %d were offered",
+                                (int)slot->out_bytes.size(), n_out));
+        for (int i = 0; i < n_out; ++i) {
+            if (out_bytes[i] != slot->out_bytes[i] || (out_bytes[i] && !out[i]))
+                return release(fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output %d: %zu bytes offered, %zu produced", i,
+                                    out_bytes[i], slot->out_bytes[i]));
+        }
+        for (int i = 0; i < n_out; ++i)
+            if (out_bytes[i]) memcpy(out[i], slot->host + slot->out_offset[i], out_bytes[i]);
+    }
+    return release(PD_OK);
+}
+
 int pd_explain(int family, const void* params, size_t params_bytes, int math_mode, const int64_t grid[3],
                const int64_t block[3], pd_launch_info* info, char* err, size_t err_cap) {
     if (!info) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "info must not be NULL");

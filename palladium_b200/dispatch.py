@@ -31,6 +31,8 @@ from .math_mode import MathMode, math_mode_ordinal
 
 __all__ = ["BoundKernel", "PendingResult", "bind"]
 
+_DIRECT_OUTPUT_BYTES = 256 << 10   # results at least this large download into page-locked arrays of their own
+
 
 def _torch():
     import torch
@@ -69,19 +71,32 @@ def _dump_source(spec: KernelSpec, math_mode) -> None:
     (directory / f"{spec.name}_{abs(hash(str(spec.family.constants))) % (1 << 48):012x}.txt").write_text(text)
 
 
-@dataclasses.dataclass
 class PendingResult:
     """A launched call whose kernels may still be executing.
 
-    `wait()` blocks on the CUDA event recorded after the device-to-host copies
-    and returns the outputs as NumPy arrays (a bare array for one output), the
-    contract of src/palladium/dispatch.py:66-86."""
+    `wait()` blocks until the call has finished and returns the outputs as NumPy
+    arrays (a bare array for one output), the contract of
+    src/palladium/dispatch.py:66-86.  A second `wait()` returns the same arrays."""
 
-    event: object
-    out_host: list
-    out_infos: tuple
+    def __init__(self, out_infos: tuple, ticket: int | None = None, event=None, out_host: list | None = None) -> None:
+        self.out_infos = out_infos
+        self._ticket = ticket          # a call submitted through pd_submit_host ...
+        self.event = event             # ... or one launched on device-resident inputs (pinned())
+        self.out_host = out_host
+        self._result = None
+        self._lock = threading.Lock()
 
-    def wait(self):
+    def _finish(self):
+        if self._ticket is not None:
+            ticket, self._ticket = self._ticket, None
+            # a kernel whose bounded wait ran out surfaces here as PalladiumError (the native call checks)
+            if self.out_host is not None:
+                _native.wait_host(ticket, [])
+                return tuple(host.numpy()[: int(np.prod(info.array_shape)) * info.dtype.itemsize].view(info.dtype)
+                             .reshape(info.array_shape) for host, info in zip(self.out_host, self.out_infos))
+            outs = [np.empty(info.array_shape, info.dtype) for info in self.out_infos]
+            _native.wait_host(ticket, [(o.ctypes.data, o.nbytes) for o in outs])
+            return tuple(outs)
         self.event.synchronize()
         # A kernel whose bounded wait ran out recorded a code instead of computing: report it
         # rather than return fields that were never written (the eager call is blocking, like
@@ -90,10 +105,24 @@ class PendingResult:
         if code:
             raise PalladiumError(f"device status {code}: a kernel's bounded wait ran out (a tile copy did not arrive "
                                  "within its limit); the outputs of this call are not valid")
-        outs = tuple(
-            host.numpy().view(info.dtype).reshape(info.array_shape) for host, info in zip(self.out_host, self.out_infos)
-        )
+        return tuple(host.numpy().view(info.dtype).reshape(info.array_shape)
+                     for host, info in zip(self.out_host, self.out_infos))
+
+    def wait(self):
+        with self._lock:
+            if self._result is None:
+                self._result = self._finish()
+            outs = self._result
         return outs[0] if len(outs) == 1 else outs
+
+    def __del__(self):
+        # a result nobody waited for still holds a slot of the library: give it back
+        ticket = getattr(self, "_ticket", None)
+        if ticket is not None:
+            try:
+                _native.wait_host(ticket, [])
+            except Exception:
+                pass
 
 
 @dataclasses.dataclass
@@ -107,13 +136,11 @@ class BoundKernel:
     math_mode: int
     threadgroup: int | tuple[int, ...] | None = None
     msl_source: str = "palladium_b200/csrc/pd_kernels.cu"
-    _in_dev: list = dataclasses.field(default_factory=list, compare=False, repr=False)
-    _in_host: list = dataclasses.field(default_factory=list, compare=False, repr=False)
-    _last_pending: PendingResult | None = dataclasses.field(default=None, compare=False, repr=False)
+    _out_sizes: list | None = dataclasses.field(default=None, compare=False, repr=False)
     _stream: object = dataclasses.field(default=None, compare=False, repr=False)
-    # Serialises upload-and-launch: concurrent launches share the input staging
-    # buffers, and each launch waits out the previous one before overwriting
-    # them.  Waiting on results stays unlocked (src/palladium/dispatch.py:121-127).
+    # Serialises the launches of `pinned()` callables, which share this kernel's stream; launches
+    # on host arrays go through the library's own slots and need no lock.  Waiting on results
+    # stays unlocked (src/palladium/dispatch.py:121-127).
     _launch_lock: threading.Lock = dataclasses.field(default_factory=threading.Lock, compare=False, repr=False)
 
     # ------------------------------------------------------------------ checks
@@ -160,31 +187,29 @@ class BoundKernel:
                     host.copy_(dev[:b], non_blocking=True)
             event = torch.cuda.Event()
             event.record(stream)
-        pending = PendingResult(event, out_host, spec.outputs)
-        self._last_pending = pending
-        return pending
+        return PendingResult(spec.outputs, event=event, out_host=out_host)
 
     def launch(self, *arrays) -> PendingResult:
         """Upload, launch and start the read-back without blocking on the
-        result.  Thread-safe: uploads are serialised per kernel, waits are not."""
+        result.  The arrays are copied before this returns, so the caller may
+        change them at once; any number of launches (up to the library's 64 slots)
+        may be in flight, each on a stream of its own.  Thread-safe."""
         arrs = self._checked(arrays)
-        torch = _require_cuda()
-        with self._launch_lock:
-            stream = self._ensure_stream(torch)
-            if self._last_pending is not None:
-                # The previous launch must be done reading the staging buffers.
-                self._last_pending.event.synchronize()
-            if not self._in_dev:
-                for arr in arrs:
-                    nbytes = max(arr.nbytes, 1)
-                    self._in_host.append(torch.empty(nbytes, dtype=torch.uint8, pin_memory=True))
-                    self._in_dev.append(torch.empty(nbytes, dtype=torch.uint8, device="cuda"))
-            with torch.cuda.stream(stream):
-                for arr, host, dev in zip(arrs, self._in_host, self._in_dev):
-                    if arr.nbytes:
-                        host.numpy()[: arr.nbytes] = arr.reshape(-1).view(np.uint8)
-                        dev[: arr.nbytes].copy_(host[: arr.nbytes], non_blocking=True)
-            return self._run(torch, self._in_dev, stream)
+        _require_cuda()
+        spec = self.spec
+        if self._out_sizes is None:
+            self._out_sizes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.outputs]
+        out_host = None
+        if sum(self._out_sizes) >= _DIRECT_OUTPUT_BYTES:
+            # Large results download straight into fresh page-locked arrays (torch's caching host
+            # allocator), which the returned NumPy arrays then view: no copy and no page faults
+            # at the wait.  Small ones come back packed in one copy and are unpacked there.
+            torch = _torch()
+            out_host = [torch.empty(max(b, 1), dtype=torch.uint8, pin_memory=True) for b in self._out_sizes]
+        ticket = _native.submit_host(spec.family.family_id, spec.params, self.math_mode, spec.grid, self.threadgroup,
+                                     [(a.ctypes.data, a.nbytes) for a in arrs], self._out_sizes,
+                                     [t.data_ptr() for t in out_host] if out_host is not None else None)
+        return PendingResult(spec.outputs, ticket=ticket, out_host=out_host)
 
     def __call__(self, *arrays):
         """Dispatch over `spec.grid` and return the outputs (NumPy)."""

@@ -155,3 +155,10 @@ def test_pointer_carrying_structs_match_the_compilers_layout(tmp_path):
         assert seen[(cname, "size")] == ctypes.sizeof(cls), cname
         for field, _ in cls._fields_:
             assert seen[(cname, field)] == getattr(cls, field).offset, (cname, field)
+
+
+def test_wait_on_an_unknown_ticket_is_invalid_argument():
+    from palladium_b200.errors import DispatchError
+
+    with pytest.raises(DispatchError, match="unknown or already retired ticket"):
+        _native.wait_host(123456789, [])

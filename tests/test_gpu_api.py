@@ -44,6 +44,46 @@ def test_second_launch_before_wait_does_not_corrupt_the_first():
     np.testing.assert_array_equal(got_b[0], oracle.lv_rk4(*b, dt=0.01, steps=200)[0])
 
 
+@pytest.mark.parametrize("n", [1000, 100_000])      # results collected at the wait / downloaded into page-locked arrays
+def test_launch_copies_its_inputs_and_many_calls_stay_in_flight(n):
+    """`launch` has read its arrays when it returns (the caller may overwrite them at once), thirty-two
+    calls in flight keep their results apart, and a second `wait` hands back the same arrays."""
+    call = H.lv_solver(n, steps=20, math_mode=SAFE)
+    ensembles = [W.lotka_volterra_ensemble(n, seed=s) for s in range(4)]
+    scratch = [a.copy() for a in ensembles[0]]
+    pending = []
+    for i in range(32):
+        for dst, src in zip(scratch, ensembles[i % 4]):
+            dst[...] = src
+        pending.append(call.launch(*scratch))
+        for dst in scratch:
+            dst[...] = np.nan            # overwritten while the call is still in flight
+    want = [oracle.lv_rk4(*e, dt=0.01, steps=20) for e in ensembles]
+    results = [h.wait() for h in reversed(pending)][::-1]
+    for i, got in enumerate(results):
+        np.testing.assert_array_equal(got[0], want[i % 4][0])
+        np.testing.assert_array_equal(got[1], want[i % 4][1])
+    assert pending[0].wait()[0] is results[0][0]
+    assert results[0][0].ctypes.data != results[4][0].ctypes.data     # equal values, separate arrays
+
+
+def test_too_many_launches_in_flight_is_an_error_and_dropped_results_free_their_slots():
+    import gc
+
+    n = 256
+    args = W.lotka_volterra_ensemble(n)
+    call = H.lv_solver(n, steps=2, math_mode=SAFE)
+    pending = [call.launch(*args) for _ in range(64)]
+    with pytest.raises(pd.DispatchError, match="in flight"):
+        call.launch(*args)
+    del pending[32:]                     # never waited for: the slots come back when the handles go
+    gc.collect()
+    more = [call.launch(*args) for _ in range(32)]
+    want = oracle.lv_rk4(*args, dt=0.01, steps=2)
+    for h in pending + more:
+        np.testing.assert_array_equal(h.wait()[0], want[0])
+
+
 def test_stepping_loop_feeds_outputs_back():
     # tests/test_dispatch_launch.py:54-72: outputs of one dispatch are the next one's inputs
     size = 64
