@@ -13,6 +13,7 @@ with the build command.
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 import threading
 from pathlib import Path
@@ -250,6 +251,19 @@ def _raise(code: int, message: bytes) -> None:
 
 
 def _arrays(grid, block):
+    """The grid and threadgroup as int64[3] arrays; cached, a call shape repeats (read-only use)."""
+    try:
+        return _arrays_cached(tuple(grid), block if block is None or isinstance(block, int) else tuple(block))
+    except TypeError:       # unhashable or unusual sequence types take the plain route
+        return _arrays_plain(grid, block)
+
+
+@functools.lru_cache(maxsize=256)
+def _arrays_cached(grid, block):
+    return _arrays_plain(grid, block)
+
+
+def _arrays_plain(grid, block):
     g = tuple(int(x) for x in grid) + (1, 1, 1)
     garr = (_i64 * 3)(*g[:3])
     if block is None:
@@ -268,6 +282,17 @@ def _buffers(ptrs_and_bytes):
     return n, ptrs, sizes
 
 
+_thread_state = threading.local()
+
+
+def _err_buffer():
+    """One message buffer per thread (the native calls write it only on failure, NUL-terminated)."""
+    buf = getattr(_thread_state, "err", None)
+    if buf is None:
+        buf = _thread_state.err = ctypes.create_string_buffer(_ERR_CAP)
+    return buf
+
+
 def launch(family: int, params: ctypes.Structure, math_mode: int, grid, block, inputs, outputs, stream: int = 0,
            workspace: tuple[int, int] | None = None) -> None:
     """pd_launch on device pointers. inputs / outputs: lists of (pointer, bytes)."""
@@ -275,7 +300,7 @@ def launch(family: int, params: ctypes.Structure, math_mode: int, grid, block, i
     garr, barr = _arrays(grid, block)
     n_in, in_ptrs, in_sizes = _buffers(inputs)
     n_out, out_ptrs, out_sizes = _buffers(outputs)
-    err = ctypes.create_string_buffer(_ERR_CAP)
+    err = _err_buffer()
     ws_ptr, ws_bytes = workspace if workspace else (None, 0)
     rc = lib.pd_launch(family, ctypes.addressof(params), ctypes.sizeof(params), math_mode, garr, barr, n_in, in_ptrs,
                        in_sizes, n_out, out_ptrs, out_sizes, ws_ptr, ws_bytes, stream or None, err, _ERR_CAP)
@@ -309,7 +334,7 @@ def submit_host(family: int, params: ctypes.Structure, math_mode: int, grid, blo
     sizes = (ctypes.c_size_t * max(n_out, 1))(*out_sizes)
     outs = (ctypes.c_void_p * max(n_out, 1))(*out_ptrs) if out_ptrs is not None else None
     ticket = ctypes.c_uint64(0)
-    err = ctypes.create_string_buffer(_ERR_CAP)
+    err = _err_buffer()
     rc = lib.pd_submit_host(family, ctypes.addressof(params), ctypes.sizeof(params), math_mode, garr, barr, n_in,
                             in_ptrs, in_sizes, n_out, outs, sizes, ctypes.byref(ticket), err, _ERR_CAP)
     if rc:
@@ -321,7 +346,7 @@ def wait_host(ticket: int, outputs) -> None:
     """pd_wait_host: block until the call behind `ticket` has finished and copy its results into
     `outputs` ((pointer, bytes) pairs; an empty list only retires the ticket)."""
     n_out, out_ptrs, out_sizes = _buffers(outputs)
-    err = ctypes.create_string_buffer(_ERR_CAP)
+    err = _err_buffer()
     rc = library().pd_wait_host(ctypes.c_uint64(ticket), n_out, out_ptrs, out_sizes, err, _ERR_CAP)
     if rc:
         _raise(rc, err.value)

@@ -136,6 +136,7 @@ class BoundKernel:
     math_mode: int
     threadgroup: int | tuple[int, ...] | None = None
     msl_source: str = "palladium_b200/csrc/pd_kernels.cu"
+    _in_sizes: list | None = dataclasses.field(default=None, compare=False, repr=False)
     _out_sizes: list | None = dataclasses.field(default=None, compare=False, repr=False)
     _stream: object = dataclasses.field(default=None, compare=False, repr=False)
     # Serialises the launches of `pinned()` callables, which share this kernel's stream; launches
@@ -169,10 +170,13 @@ class BoundKernel:
     def _run(self, torch, in_dev: list, stream) -> PendingResult:
         """Launch on device inputs; copy the outputs into fresh pinned buffers."""
         spec = self.spec
-        out_bytes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.outputs]
+        if self._in_sizes is None:
+            self._in_sizes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.inputs]
+        if self._out_sizes is None:
+            self._out_sizes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.outputs]
+        in_bytes, out_bytes = self._in_sizes, self._out_sizes
         with torch.cuda.stream(stream):
             out_dev = [torch.empty(max(b, 1), dtype=torch.uint8, device="cuda") for b in out_bytes]
-            in_bytes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.inputs]
             _native.launch(
                 spec.family.family_id, spec.params, self.math_mode, spec.grid, self.threadgroup,
                 [(t.data_ptr(), b) for t, b in zip(in_dev, in_bytes)],
@@ -248,13 +252,20 @@ class BoundKernel:
         spec = self.spec
         if len(inputs) != len(spec.inputs):
             raise DispatchError(f"kernel takes {len(spec.inputs)} arrays, got {len(inputs)}")
-        in_bytes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.inputs]
-        out_bytes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.outputs]
+        if self._in_sizes is None:
+            self._in_sizes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.inputs]
+        if self._out_sizes is None:
+            self._out_sizes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.outputs]
+        in_bytes, out_bytes = self._in_sizes, self._out_sizes
         current = torch.cuda.current_device()
         check_device_tensors("argument", inputs, in_bytes, current)
-        st = stream if stream is not None else torch.cuda.current_stream()
+        if stream is not None:
+            raw_stream = stream.cuda_stream
+        else:
+            raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)   # the handle alone, without a Stream object
+            raw_stream = raw(current) if raw is not None else torch.cuda.current_stream().cuda_stream
         if outputs is None:
-            with torch.cuda.stream(st):
+            with torch.cuda.stream(stream if stream is not None else torch.cuda.current_stream()):
                 outputs = [torch.empty(max(b, 1), dtype=torch.uint8, device="cuda") for b in out_bytes]
         elif len(outputs) != len(out_bytes):
             raise DispatchError(f"kernel produces {len(out_bytes)} arrays, got {len(outputs)} output tensors")
@@ -266,7 +277,7 @@ class BoundKernel:
             spec.family.family_id, spec.params, self.math_mode, spec.grid, self.threadgroup,
             [(t.data_ptr(), b) for t, b in zip(inputs, in_bytes)],
             [(t.data_ptr(), b) for t, b in zip(outputs, out_bytes)],
-            stream=st.cuda_stream,
+            stream=raw_stream,
             workspace=(workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None else None,
         )
         return outputs

@@ -55,6 +55,20 @@ def _is_jax_value(x) -> bool:
     return type(x).__module__.startswith(("jax", "jaxlib"))
 
 
+_DTYPE_TABLES: list = []
+_SMALL_HOST_CALL_BYTES = 256 << 10
+
+
+def _torch_dtype_tables(torch):
+    """(torch dtype -> NumPy dtype name, and back), built once."""
+    if not _DTYPE_TABLES:
+        to_np = {torch.float32: "float32", torch.int32: "int32", torch.uint32: "uint32", torch.float64: "float64",
+                 torch.uint8: "uint8"}
+        to_torch = {"float32": torch.float32, "int32": torch.int32, "uint32": torch.uint32, "float64": torch.float64}
+        _DTYPE_TABLES.append((to_np, to_torch))
+    return _DTYPE_TABLES[0]
+
+
 def _pinned_empty(shape, dtype) -> np.ndarray:
     """Output array in page-locked host memory (torch's caching host allocator),
     so the device-to-host copy is a true asynchronous DMA and the chunks of a
@@ -166,12 +180,9 @@ class FfiCallable:
     def _call_torch(self, args, out=None):
         import torch
 
-        np_dtype = {torch.float32: "float32", torch.int32: "int32", torch.uint32: "uint32",
-                    torch.float64: "float64", torch.uint8: "uint8"}
+        np_dtype, torch_dtype = _torch_dtype_tables(torch)
         shapes = tuple((tuple(a.shape), np_dtype.get(a.dtype, str(a.dtype))) for a in args)
         spec, bound = self._entry(shapes)
-        torch_dtype = {"float32": torch.float32, "int32": torch.int32, "uint32": torch.uint32,
-                       "float64": torch.float64}
         device = args[0].device if args else torch.device("cuda", torch.cuda.current_device())
         if out is not None:
             outs = list(out) if isinstance(out, (list, tuple)) else [out]
@@ -192,6 +203,15 @@ class FfiCallable:
         arrays = [np.ascontiguousarray(a) for a in args]
         shapes = tuple((a.shape, a.dtype.name) for a in arrays)
         spec, _ = self._entry(shapes)
+        out_bytes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.outputs]
+        if sum(a.nbytes for a in arrays) + sum(out_bytes) < _SMALL_HOST_CALL_BYTES:
+            # A small call: inputs packed into one upload, results into one download (the library's
+            # slot path), ordinary result arrays -- cheaper than page-locked ones at this size.
+            outs = [np.empty(info.array_shape, info.dtype) for info in spec.outputs]
+            ticket = _native.submit_host(spec.family.family_id, spec.params, self._math_mode, spec.grid,
+                                         self._threadgroup, [(a.ctypes.data, a.nbytes) for a in arrays], out_bytes)
+            _native.wait_host(ticket, [(o.ctypes.data, o.nbytes) for o in outs])
+            return outs[0] if len(outs) == 1 else tuple(outs)
         outs = [_pinned_empty(info.array_shape, info.dtype) for info in spec.outputs]
         _native.dispatch_host(
             spec.family.family_id, spec.params, self._math_mode, spec.grid, self._threadgroup,
