@@ -208,6 +208,19 @@ def cpu_family_baselines() -> dict:
     sec, _ = timed(lambda: oracle.gray_scott(u, v, steps=steps))
     out["gray_scott"] = {"sample": f"{size} x {size}, {steps} steps", "seconds": sec,
                          "cell_steps_per_s": size * size * steps / sec}
+    # the job of the reference's CPU comparison (benchmarks/bench_ensembles.py:88-118: Tsit5 under a step
+    # controller, rtol 1e-6, atol 1e-8, t = 5, n = 10 000 and 100 000), on the CPU restatement of the same pair
+    from oracle import custom_ode as oracle_custom
+    import bench_families as bf
+
+    for n in (10_000, 100_000):
+        ens = bf.reference_benchmark_ensemble(n)
+        kw = dict(method="tsit5", t1=5.0, rtol=1e-6, atol=1e-8, dt0=0.01, max_steps=bf.LV_TSIT5_MAX_STEPS)
+        oracle_custom.erk(bf.LV_RHS, 2, 4, [a[:256] for a in ens], **kw)       # builds the shared object
+        sec, res = timed(lambda: oracle_custom.erk(bf.LV_RHS, 2, 4, ens, **kw))
+        out[f"lv_tsit5_n={n}"] = {"sample": f"{n} trajectories to t = 5 (the whole job), loop of {kw['max_steps']} iterations "
+                                            "(no trajectory needs more than 48)",
+                                  "seconds": sec, "ms": sec * 1e3, "accepted_steps_mean": float(res[5].mean())}
     n, steps = 8192, 500
     _, pairs = W.kepler_ensemble(n)
     sec, _ = timed(lambda: oracle.kepler_rk4_df32(pairs, dt=1e-3, steps=steps))

@@ -236,7 +236,8 @@ def bench_lv_df32(n: int, steps: int, warmup: int = 1, iters: int = 3, fma_peak:
 # The Lotka-Volterra right-hand side as a caller would hand it to `custom_ode`:
 # in the reference's expression order, and factored so that each line is one
 # multiply by a fused multiply-add.
-CUSTOM_LV_RHS = "dy[0] = p[0]*y[0] - (p[1]*y[0])*y[1];\ndy[1] = (p[2]*y[0])*y[1] - p[3]*y[1];"
+CUSTOM_LV_TSIT5_MAX_STEPS = 64   # iterations of the adaptive loop: every trajectory of the benchmark ensembles ends within 48
+LV_RHS = "dy[0] = p[0]*y[0] - (p[1]*y[0])*y[1];\ndy[1] = (p[2]*y[0])*y[1] - p[3]*y[1];"
 CUSTOM_LV_RHS_FACTORED = "dy[0] = y[0]*fmaf(-p[1], y[1], p[0]);\ndy[1] = y[1]*fmaf(p[2], y[0], -p[3]);"
 
 
@@ -263,6 +264,53 @@ def bench_custom_ode(n: int, steps: int, math_mode: str = "fast", rhs: str = CUS
     if fma_peak:
         res["frac_of_fp32_peak"] = res["trajectory_steps_per_s"] * 58 / fma_peak
     return res
+
+
+LV_TSIT5_MAX_STEPS = 64   # iterations of the adaptive loop: every trajectory of the benchmark ensembles ends within 48
+LV_RHS = "dy[0] = p[0]*y[0] - (p[1]*y[0])*y[1];\ndy[1] = (p[2]*y[0])*y[1] - p[3]*y[1];"
+
+
+def reference_benchmark_ensemble(n: int, seed: int = 17):
+    """The ensemble of the reference's benchmark suite (benchmarks/bench_ensembles.py:29-38): its
+    ranges and draw order, not those of the named throughput configuration."""
+    rng = np.random.default_rng(seed)
+    ranges = ((0.8, 1.2), (0.8, 1.2), (0.9, 1.3), (0.3, 0.5), (0.08, 0.12), (0.3, 0.5))
+    return tuple(rng.uniform(lo, hi, n).astype(np.float32) for lo, hi in ranges)
+
+
+def bench_ensembles(repeats: int = 30) -> dict:
+    """The reference's own benchmark definitions (benchmarks/bench_ensembles.py:24-26,78-118):
+    the Lotka-Volterra ensemble at n = 10 000 and 100 000, dt 0.01, 500 steps, wall-clock ms of the
+    eager call on host arrays with everything compiled beforehand (`bench_lv_palladium`); and its
+    CPU comparison's job -- Tsit5 to t = 5 at rtol 1e-6, atol 1e-8 (`bench_lv_diffrax`) -- through
+    `custom_ode(method="tsit5")` on the GPU.  The reference commits no results of either."""
+    from palladium_b200 import cuda_call, families, pl
+
+    spec_1 = pl.BlockSpec((1,), lambda i: (i,))
+    out = {"definition": "benchmarks/bench_ensembles.py: dt 0.01, 500 steps, wall-clock ms per solve, medians"}
+    for n in (10_000, 100_000):
+        args = reference_benchmark_ensemble(n)
+        rk4 = cuda_call(families.lv_rk4(0.01, 500), grid=(n,), in_specs=[spec_1] * 6, out_specs=(spec_1, spec_1),
+                        out_shape=(_shaped((n,)), _shaped((n,))), math_mode="fast")
+        tsit5 = cuda_call(families.custom_ode(LV_RHS, 2, 4, method="tsit5", t1=5.0, rtol=1e-6, atol=1e-8, dt0=0.01,
+                                              max_steps=LV_TSIT5_MAX_STEPS),
+                          grid=(n,), in_specs=[spec_1] * 6, out_specs=(spec_1,) * 6,
+                          out_shape=tuple(_shaped((n,)) for _ in range(6)), math_mode="fast")
+
+        def median_ms(call):
+            call(*args)
+            samples = []
+            for _ in range(repeats):
+                t0 = time.perf_counter()
+                res = call(*args)
+                samples.append(time.perf_counter() - t0)
+            return float(np.median(samples)) * 1e3, res
+
+        ms_rk4, _ = median_ms(rk4)
+        ms_t5, res = median_ms(tsit5)
+        out[f"n={n}"] = {"rk4_500_steps_eager_ms": ms_rk4, "tsit5_rtol1e-6_eager_ms": ms_t5,
+                         "tsit5_accepted_steps_mean": float(res[5].mean()), "tsit5_all_reached_t1": bool((res[0] == 5.0).all())}
+    return out
 
 
 def fixed_costs(calls: int = 300) -> dict:
@@ -346,6 +394,7 @@ def quick_summary(named: bool = True) -> dict:
     out["custom_ode_lv"] = bench_custom_ode(1 << 22, 1000, "fast", fma_peak=fma_peak)
     out["vdp_tsit5_safe"] = bench_vdp_pair(1 << 18, "tsit5", "safe")
     out["fixed_costs"] = fixed_costs()
+    out["bench_ensembles"] = bench_ensembles()
     out.update(named_rk4_modes(fma_peak))
     if named:
         out.update(named_configs(fma_peak, int_peak))
