@@ -323,10 +323,14 @@ PD_API int pd_dispatch_host(int family, const void* params, size_t params_bytes,
  * arrays up front: they must be page-locked (an ordinary array would make the
  * submission wait for the kernels) and stay alive until the wait, which is then
  * called with n_out == 0 and copies nothing.
+ * `in_on_device` is NULL, or says per input (non-zero) that `in[i]` is device memory
+ * already -- inputs uploaded once and used by many calls, the reference's
+ * `call.pin(*arrays)` (src/palladium/dispatch.py:230-255); such memory must stay
+ * alive and unchanged until the wait.
  * At most 64 calls may be in flight in a process; every ticket must be waited for. */
 PD_API int pd_submit_host(int family, const void* params, size_t params_bytes, int math_mode,
                    const int64_t grid[3], const int64_t block[3],
-                   int n_in, const void* const* in, const size_t* in_bytes,
+                   int n_in, const void* const* in, const size_t* in_bytes, const int* in_on_device,
                    int n_out, void* const* out, const size_t* out_bytes, uint64_t* ticket,
                    char* err, size_t err_cap);
 PD_API int pd_wait_host(uint64_t ticket, int n_out, void* const* out, const size_t* out_bytes,

@@ -167,7 +167,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.pd_dispatch_host.restype = ci
     lib.pd_dispatch_host.argtypes = [ci, vp, sz, ci, i64p, i64p, ci, vpp, szp, ci, vpp, szp, cp, sz]
     lib.pd_submit_host.restype = ci
-    lib.pd_submit_host.argtypes = [ci, vp, sz, ci, i64p, i64p, ci, vpp, szp, ci, vpp, szp, ctypes.POINTER(ctypes.c_uint64), cp, sz]
+    lib.pd_submit_host.argtypes = [ci, vp, sz, ci, i64p, i64p, ci, vpp, szp, ctypes.POINTER(ci), ci, vpp, szp, ctypes.POINTER(ctypes.c_uint64), cp, sz]
     lib.pd_wait_host.restype = ci
     lib.pd_wait_host.argtypes = [ctypes.c_uint64, ci, vpp, szp, cp, sz]
     lib.pd_explain.restype = ci
@@ -322,11 +322,11 @@ def dispatch_host(family: int, params: ctypes.Structure, math_mode: int, grid, b
 
 
 def submit_host(family: int, params: ctypes.Structure, math_mode: int, grid, block, inputs, out_sizes,
-                out_ptrs=None) -> int:
+                out_ptrs=None, inputs_on_device: bool = False) -> int:
     """pd_submit_host: queue a call on host pointers without waiting for it; returns the ticket.
     inputs: (pointer, bytes) pairs, copied before the call returns; out_sizes: bytes per output;
     out_ptrs: page-locked result arrays to download into directly (else the results are collected
-    by wait_host)."""
+    by wait_host); inputs_on_device: the input pointers are device memory (uploaded earlier)."""
     lib = library()
     garr, barr = _arrays(grid, block)
     n_in, in_ptrs, in_sizes = _buffers(inputs)
@@ -335,8 +335,9 @@ def submit_host(family: int, params: ctypes.Structure, math_mode: int, grid, blo
     outs = (ctypes.c_void_p * max(n_out, 1))(*out_ptrs) if out_ptrs is not None else None
     ticket = ctypes.c_uint64(0)
     err = _err_buffer()
+    on_device = (ctypes.c_int * max(n_in, 1))(*([1] * n_in)) if inputs_on_device else None
     rc = lib.pd_submit_host(family, ctypes.addressof(params), ctypes.sizeof(params), math_mode, garr, barr, n_in,
-                            in_ptrs, in_sizes, n_out, outs, sizes, ctypes.byref(ticket), err, _ERR_CAP)
+                            in_ptrs, in_sizes, on_device, n_out, outs, sizes, ctypes.byref(ticket), err, _ERR_CAP)
     if rc:
         _raise(rc, err.value)
     return ticket.value

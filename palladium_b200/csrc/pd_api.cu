@@ -1375,8 +1375,9 @@ size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 extern "C" {
 
 int pd_submit_host(int family, const void* params, size_t params_bytes, int math_mode, const int64_t grid[3],
-                   const int64_t block[3], int n_in, const void* const* in, const size_t* in_bytes, int n_out,
-                   void* const* out, const size_t* out_bytes, uint64_t* ticket, char* err, size_t err_cap) {
+                   const int64_t block[3], int n_in, const void* const* in, const size_t* in_bytes,
+                   const int* in_on_device, int n_out, void* const* out, const size_t* out_bytes, uint64_t* ticket,
+                   char* err, size_t err_cap) {
     DeviceFacts dev = device_facts();
     if (!dev.present)
         return fail(PD_ERR_CUDA, err, err_cap, "no CUDA device is available: libpalladium_cuda has no CPU fallback");
@@ -1389,7 +1390,10 @@ int pd_submit_host(int family, const void* params, size_t params_bytes, int math
         if (in_bytes[i] && !in[i]) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "input %d: NULL pointer", i);
     size_t total = 0;
     std::vector<size_t> in_offset(n_in), out_offset(n_out);
-    for (int i = 0; i < n_in; ++i) { in_offset[i] = total; total += align256(in_bytes[i]); }
+    for (int i = 0; i < n_in; ++i) {   // inputs that already live on the device take no room in the slot
+        in_offset[i] = total;
+        if (!(in_on_device && in_on_device[i])) total += align256(in_bytes[i]);
+    }
     const size_t out_begin = total;
     for (int i = 0; i < n_out; ++i) { out_offset[i] = total; total += align256(out_bytes[i]); }
     if (total == 0) total = 256;
@@ -1445,7 +1449,7 @@ int pd_submit_host(int family, const void* params, size_t params_bytes, int math
     if (out_begin < ((size_t)256 << 10)) {
         // small inputs: packed into the slot's block and uploaded by one copy
         for (int i = 0; i < n_in; ++i)
-            if (in_bytes[i]) memcpy(slot->host + in_offset[i], in[i], in_bytes[i]);
+            if (in_bytes[i] && !(in_on_device && in_on_device[i])) memcpy(slot->host + in_offset[i], in[i], in_bytes[i]);
         if (out_begin) {
             if ((e = cudaMemcpyAsync(slot->dev, slot->host, out_begin, cudaMemcpyHostToDevice, slot->stream)) != cudaSuccess)
                 return cuda_fail(e, "cudaMemcpyAsync (upload)");
@@ -1455,7 +1459,7 @@ int pd_submit_host(int family, const void* params, size_t params_bytes, int math
         // source, so the caller's array is free again without a second pass over it on this thread;
         // page-locked or managed sources would be read asynchronously and go through the slot's block.
         for (int i = 0; i < n_in; ++i) {
-            if (!in_bytes[i]) continue;
+            if (!in_bytes[i] || (in_on_device && in_on_device[i])) continue;
             cudaPointerAttributes attr;
             const bool pageable = cudaPointerGetAttributes(&attr, in[i]) == cudaSuccess &&
                                   attr.type == cudaMemoryTypeUnregistered;
@@ -1474,7 +1478,7 @@ int pd_submit_host(int family, const void* params, size_t params_bytes, int math
     }
     std::vector<const void*> d_in(n_in);
     std::vector<void*> d_out(n_out);
-    for (int i = 0; i < n_in; ++i) d_in[i] = slot->dev + in_offset[i];
+    for (int i = 0; i < n_in; ++i) d_in[i] = (in_on_device && in_on_device[i]) ? in[i] : slot->dev + in_offset[i];
     for (int i = 0; i < n_out; ++i) d_out[i] = slot->dev + out_offset[i];
     int rc = launch_impl(family, params, params_bytes, math_mode, grid, block, n_in, d_in.data(), in_bytes, n_out,
                          d_out.data(), out_bytes, nullptr, 0, slot->stream, err, err_cap);

@@ -78,35 +78,24 @@ class PendingResult:
     arrays (a bare array for one output), the contract of
     src/palladium/dispatch.py:66-86.  A second `wait()` returns the same arrays."""
 
-    def __init__(self, out_infos: tuple, ticket: int | None = None, event=None, out_host: list | None = None) -> None:
+    def __init__(self, out_infos: tuple, ticket: int, out_host: list | None = None) -> None:
         self.out_infos = out_infos
-        self._ticket = ticket          # a call submitted through pd_submit_host ...
-        self.event = event             # ... or one launched on device-resident inputs (pinned())
-        self.out_host = out_host
+        self._ticket = ticket          # the library's handle of the call in flight (pd_submit_host)
+        self.out_host = out_host       # page-locked arrays the results download into, or None (collected at the wait)
         self._result = None
         self._lock = threading.Lock()
 
     def _finish(self):
-        if self._ticket is not None:
-            ticket, self._ticket = self._ticket, None
-            # a kernel whose bounded wait ran out surfaces here as PalladiumError (the native call checks)
-            if self.out_host is not None:
-                _native.wait_host(ticket, [])
-                return tuple(host.numpy()[: int(np.prod(info.array_shape)) * info.dtype.itemsize].view(info.dtype)
-                             .reshape(info.array_shape) for host, info in zip(self.out_host, self.out_infos))
-            outs = [np.empty(info.array_shape, info.dtype) for info in self.out_infos]
-            _native.wait_host(ticket, [(o.ctypes.data, o.nbytes) for o in outs])
-            return tuple(outs)
-        self.event.synchronize()
-        # A kernel whose bounded wait ran out recorded a code instead of computing: report it
-        # rather than return fields that were never written (the eager call is blocking, like
-        # mr_dispatch in the reference, so this is where its status surfaces).
-        code = _native.device_status()
-        if code:
-            raise PalladiumError(f"device status {code}: a kernel's bounded wait ran out (a tile copy did not arrive "
-                                 "within its limit); the outputs of this call are not valid")
-        return tuple(host.numpy().view(info.dtype).reshape(info.array_shape)
-                     for host, info in zip(self.out_host, self.out_infos))
+        ticket, self._ticket = self._ticket, None
+        # A kernel whose bounded wait ran out recorded a code instead of computing: the native wait
+        # reports it (PalladiumError) rather than hand over fields that were never written.
+        if self.out_host is not None:
+            _native.wait_host(ticket, [])
+            return tuple(host.numpy()[: int(np.prod(info.array_shape)) * info.dtype.itemsize].view(info.dtype)
+                         .reshape(info.array_shape) for host, info in zip(self.out_host, self.out_infos))
+        outs = [np.empty(info.array_shape, info.dtype) for info in self.out_infos]
+        _native.wait_host(ticket, [(o.ctypes.data, o.nbytes) for o in outs])
+        return tuple(outs)
 
     def wait(self):
         with self._lock:
@@ -138,11 +127,9 @@ class BoundKernel:
     msl_source: str = "palladium_b200/csrc/pd_kernels.cu"
     _in_sizes: list | None = dataclasses.field(default=None, compare=False, repr=False)
     _out_sizes: list | None = dataclasses.field(default=None, compare=False, repr=False)
-    _stream: object = dataclasses.field(default=None, compare=False, repr=False)
-    # Serialises the launches of `pinned()` callables, which share this kernel's stream; launches
-    # on host arrays go through the library's own slots and need no lock.  Waiting on results
-    # stays unlocked (src/palladium/dispatch.py:121-127).
-    _launch_lock: threading.Lock = dataclasses.field(default_factory=threading.Lock, compare=False, repr=False)
+    # Launches go through the library's slot pool (a stream and an event per call in flight), which
+    # serialises what it must itself: no lock is held here, neither to launch nor to wait
+    # (src/palladium/dispatch.py:121-127 holds one per kernel for launching).
 
     # ------------------------------------------------------------------ checks
     def _checked(self, arrays) -> list[np.ndarray]:
@@ -161,38 +148,7 @@ class BoundKernel:
             out.append(np.ascontiguousarray(arr))
         return out
 
-    def _ensure_stream(self, torch):
-        if self._stream is None:
-            self._stream = torch.cuda.Stream()
-        return self._stream
-
     # ------------------------------------------------------------------ launch
-    def _run(self, torch, in_dev: list, stream) -> PendingResult:
-        """Launch on device inputs; copy the outputs into fresh pinned buffers."""
-        spec = self.spec
-        if self._in_sizes is None:
-            self._in_sizes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.inputs]
-        if self._out_sizes is None:
-            self._out_sizes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.outputs]
-        in_bytes, out_bytes = self._in_sizes, self._out_sizes
-        with torch.cuda.stream(stream):
-            out_dev = [torch.empty(max(b, 1), dtype=torch.uint8, device="cuda") for b in out_bytes]
-            _native.launch(
-                spec.family.family_id, spec.params, self.math_mode, spec.grid, self.threadgroup,
-                [(t.data_ptr(), b) for t, b in zip(in_dev, in_bytes)],
-                [(t.data_ptr(), b) for t, b in zip(out_dev, out_bytes)],
-                stream=stream.cuda_stream,
-            )
-            # Fresh per call: a caller may still hold the arrays of an earlier,
-            # not yet waited-on result (src/palladium/dispatch.py:180-186).
-            out_host = [torch.empty(b, dtype=torch.uint8, pin_memory=True) for b in out_bytes]
-            for host, dev, b in zip(out_host, out_dev, out_bytes):
-                if b:
-                    host.copy_(dev[:b], non_blocking=True)
-            event = torch.cuda.Event()
-            event.record(stream)
-        return PendingResult(spec.outputs, event=event, out_host=out_host)
-
     def launch(self, *arrays) -> PendingResult:
         """Upload, launch and start the read-back without blocking on the
         result.  The arrays are copied before this returns, so the caller may
@@ -200,6 +156,9 @@ class BoundKernel:
         may be in flight, each on a stream of its own.  Thread-safe."""
         arrs = self._checked(arrays)
         _require_cuda()
+        return self._submit([(a.ctypes.data, a.nbytes) for a in arrs], False)
+
+    def _submit(self, inputs, on_device: bool) -> PendingResult:
         spec = self.spec
         if self._out_sizes is None:
             self._out_sizes = [int(np.prod(info.array_shape)) * info.dtype.itemsize for info in spec.outputs]
@@ -211,8 +170,8 @@ class BoundKernel:
             torch = _torch()
             out_host = [torch.empty(max(b, 1), dtype=torch.uint8, pin_memory=True) for b in self._out_sizes]
         ticket = _native.submit_host(spec.family.family_id, spec.params, self.math_mode, spec.grid, self.threadgroup,
-                                     [(a.ctypes.data, a.nbytes) for a in arrs], self._out_sizes,
-                                     [t.data_ptr() for t in out_host] if out_host is not None else None)
+                                     inputs, self._out_sizes,
+                                     [t.data_ptr() for t in out_host] if out_host is not None else None, on_device)
         return PendingResult(spec.outputs, ticket=ticket, out_host=out_host)
 
     def __call__(self, *arrays):
@@ -225,16 +184,14 @@ class BoundKernel:
         passed arrays is not observed (src/palladium/dispatch.py:230-255)."""
         arrs = self._checked(arrays)
         torch = _require_cuda()
-        stream = self._ensure_stream(torch)
-        with torch.cuda.stream(stream):
-            resident = [torch.from_numpy(a.reshape(-1).view(np.uint8).copy()).to("cuda", non_blocking=False)
-                        if a.nbytes else torch.empty(1, dtype=torch.uint8, device="cuda") for a in arrs]
-        stream.synchronize()
+        resident = [torch.from_numpy(a.reshape(-1).view(np.uint8).copy()).to("cuda", non_blocking=False)
+                    if a.nbytes else torch.empty(1, dtype=torch.uint8, device="cuda") for a in arrs]
+        torch.cuda.current_stream().synchronize()
 
-        def call():
-            with self._launch_lock:
-                pending = self._run(torch, resident, stream)
-            return pending.wait()
+        pointers = [(t.data_ptr(), a.nbytes) for t, a in zip(resident, arrs)]
+
+        def call(_resident=resident):     # the default argument keeps the device copies alive with the callable
+            return self._submit(pointers, True).wait()
 
         return call
 
