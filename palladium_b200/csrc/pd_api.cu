@@ -1355,7 +1355,7 @@ struct AsyncSlot {
     cudaEvent_t done = nullptr;
     unsigned char* host = nullptr;
     unsigned char* dev = nullptr;
-    size_t capacity = 0;
+    size_t capacity = 0, host_capacity = 0;   // bytes of the device block and of the host block
     size_t out_begin = 0;
     bool direct_out = false;   // the results went straight to arrays the caller named at submission
     std::vector<size_t> out_offset, out_bytes;
@@ -1388,22 +1388,50 @@ int pd_submit_host(int family, const void* params, size_t params_bytes, int math
         return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "buffer arrays must not be NULL");
     for (int i = 0; i < n_in; ++i)
         if (in_bytes[i] && !in[i]) return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "input %d: NULL pointer", i);
-    size_t total = 0;
-    std::vector<size_t> in_offset(n_in), out_offset(n_out);
-    for (int i = 0; i < n_in; ++i) {   // inputs that already live on the device take no room in the slot
+    // Device block: every input that is not on the device already, then the outputs.  Host block:
+    // the inputs that are staged (all of them when they are small and go up in one copy; of large
+    // ones only those that are not ordinary pageable memory), then the outputs unless the caller
+    // named page-locked result arrays.
+    auto on_device = [&](int i) { return in_on_device && in_on_device[i]; };
+    size_t host_in_bytes = 0;
+    for (int i = 0; i < n_in; ++i)
+        if (!on_device(i)) host_in_bytes += in_bytes[i];
+    const bool packed_upload = host_in_bytes < ((size_t)256 << 10);
+    std::vector<size_t> in_offset(n_in), in_host_offset(n_in), out_offset(n_out);
+    std::vector<char> staged(n_in, 0);
+    size_t total = 0, host_total = 0;
+    for (int i = 0; i < n_in; ++i) {
         in_offset[i] = total;
-        if (!(in_on_device && in_on_device[i])) total += align256(in_bytes[i]);
+        in_host_offset[i] = host_total;
+        if (on_device(i) || !in_bytes[i]) continue;
+        total += align256(in_bytes[i]);
+        bool stage = packed_upload;
+        if (!stage) {
+            // A copy from ordinary (pageable) memory returns once the driver has staged the source, so
+            // the caller's array is free again without a second pass over it on this thread;
+            // page-locked or managed sources would be read asynchronously and go through the slot.
+            cudaPointerAttributes attr;
+            stage = !(cudaPointerGetAttributes(&attr, in[i]) == cudaSuccess && attr.type == cudaMemoryTypeUnregistered);
+            cudaGetLastError();
+        }
+        staged[i] = stage ? 1 : 0;
+        if (stage) host_total += align256(in_bytes[i]);
     }
-    const size_t out_begin = total;
-    for (int i = 0; i < n_out; ++i) { out_offset[i] = total; total += align256(out_bytes[i]); }
+    const size_t out_begin = total, host_out_begin = host_total;
+    for (int i = 0; i < n_out; ++i) {
+        out_offset[i] = total;
+        total += align256(out_bytes[i]);
+        if (!out) host_total += align256(out_bytes[i]);
+    }
     if (total == 0) total = 256;
+    if (host_total == 0) host_total = 256;
 
     AsyncSlot* slot = nullptr;
     {
         std::lock_guard<std::mutex> lock(g_async_mutex);
         std::vector<AsyncSlot*>& slots = async_slots();
         for (AsyncSlot* s : slots)   // a free slot that is large enough, else any free slot (it grows below)
-            if (!s->busy && s->device == dev.device && s->capacity >= total) { slot = s; break; }
+            if (!s->busy && s->device == dev.device && s->capacity >= total && s->host_capacity >= host_total) { slot = s; break; }
         if (!slot)
             for (AsyncSlot* s : slots)
                 if (!s->busy && s->device == dev.device) { slot = s; break; }
@@ -1435,40 +1463,34 @@ int pd_submit_host(int family, const void* params, size_t params_bytes, int math
         if ((e = cudaEventCreateWithFlags(&slot->done, cudaEventDisableTiming)) != cudaSuccess)
             return cuda_fail(e, "cudaEventCreateWithFlags");
     }
+    // the slot is free, so nothing of an earlier call still uses its blocks
     if (slot->capacity < total) {
-        // the slot is free, so nothing of an earlier call still uses its blocks
-        if (slot->host) { cudaFreeHost(slot->host); slot->host = nullptr; }
         if (slot->dev) { cudaFree(slot->dev); slot->dev = nullptr; }
         slot->capacity = 0;
         const size_t want = total < 65536 ? 65536 : total;
-        if ((e = cudaHostAlloc((void**)&slot->host, want, cudaHostAllocDefault)) != cudaSuccess)
-            return cuda_fail(e, "cudaHostAlloc");
         if ((e = cudaMalloc((void**)&slot->dev, want)) != cudaSuccess) return cuda_fail(e, "cudaMalloc");
         slot->capacity = want;
     }
-    if (out_begin < ((size_t)256 << 10)) {
-        // small inputs: packed into the slot's block and uploaded by one copy
-        for (int i = 0; i < n_in; ++i)
-            if (in_bytes[i] && !(in_on_device && in_on_device[i])) memcpy(slot->host + in_offset[i], in[i], in_bytes[i]);
+    if (slot->host_capacity < host_total) {
+        if (slot->host) { cudaFreeHost(slot->host); slot->host = nullptr; }
+        slot->host_capacity = 0;
+        const size_t want = host_total < 65536 ? 65536 : host_total;
+        if ((e = cudaHostAlloc((void**)&slot->host, want, cudaHostAllocDefault)) != cudaSuccess)
+            return cuda_fail(e, "cudaHostAlloc");
+        slot->host_capacity = want;
+    }
+    for (int i = 0; i < n_in; ++i)
+        if (staged[i]) memcpy(slot->host + in_host_offset[i], in[i], in_bytes[i]);
+    if (packed_upload) {
+        // small inputs sit in the host block in the order and spacing of the device block: one copy
         if (out_begin) {
             if ((e = cudaMemcpyAsync(slot->dev, slot->host, out_begin, cudaMemcpyHostToDevice, slot->stream)) != cudaSuccess)
                 return cuda_fail(e, "cudaMemcpyAsync (upload)");
         }
     } else {
-        // Large inputs: a copy from ordinary (pageable) memory returns once the driver has staged the
-        // source, so the caller's array is free again without a second pass over it on this thread;
-        // page-locked or managed sources would be read asynchronously and go through the slot's block.
         for (int i = 0; i < n_in; ++i) {
-            if (!in_bytes[i] || (in_on_device && in_on_device[i])) continue;
-            cudaPointerAttributes attr;
-            const bool pageable = cudaPointerGetAttributes(&attr, in[i]) == cudaSuccess &&
-                                  attr.type == cudaMemoryTypeUnregistered;
-            cudaGetLastError();
-            const void* src = in[i];
-            if (!pageable) {
-                memcpy(slot->host + in_offset[i], in[i], in_bytes[i]);
-                src = slot->host + in_offset[i];
-            }
+            if (on_device(i) || !in_bytes[i]) continue;
+            const void* src = staged[i] ? (const void*)(slot->host + in_host_offset[i]) : in[i];
             if ((e = cudaMemcpyAsync(slot->dev + in_offset[i], src, in_bytes[i], cudaMemcpyHostToDevice, slot->stream)) !=
                 cudaSuccess) {
                 cudaStreamSynchronize(slot->stream);
@@ -1478,7 +1500,7 @@ int pd_submit_host(int family, const void* params, size_t params_bytes, int math
     }
     std::vector<const void*> d_in(n_in);
     std::vector<void*> d_out(n_out);
-    for (int i = 0; i < n_in; ++i) d_in[i] = (in_on_device && in_on_device[i]) ? in[i] : slot->dev + in_offset[i];
+    for (int i = 0; i < n_in; ++i) d_in[i] = on_device(i) ? in[i] : slot->dev + in_offset[i];
     for (int i = 0; i < n_out; ++i) d_out[i] = slot->dev + out_offset[i];
     int rc = launch_impl(family, params, params_bytes, math_mode, grid, block, n_in, d_in.data(), in_bytes, n_out,
                          d_out.data(), out_bytes, nullptr, 0, slot->stream, err, err_cap);
@@ -1501,8 +1523,9 @@ int pd_submit_host(int family, const void* params, size_t params_bytes, int math
             }
         }
     } else if (total > out_begin && n_out > 0) {
-        if ((e = cudaMemcpyAsync(slot->host + out_begin, slot->dev + out_begin, total - out_begin, cudaMemcpyDeviceToHost,
-                                 slot->stream)) != cudaSuccess) {
+        // the outputs keep the spacing of the device block: one copy, unpacked at the wait
+        if ((e = cudaMemcpyAsync(slot->host + host_out_begin, slot->dev + out_begin, total - out_begin,
+                                 cudaMemcpyDeviceToHost, slot->stream)) != cudaSuccess) {
             cudaStreamSynchronize(slot->stream);
             return cuda_fail(e, "cudaMemcpyAsync (download)");
         }
@@ -1512,6 +1535,7 @@ int pd_submit_host(int family, const void* params, size_t params_bytes, int math
         return cuda_fail(e, "cudaEventRecord");
     }
     slot->out_begin = out_begin;
+    for (size_t& o : out_offset) o = o - out_begin + host_out_begin;   // where each result lies in the host block
     slot->out_offset = out_offset;
     slot->out_bytes.assign(out_bytes, out_bytes + n_out);
     slot->direct_out = out != nullptr;
@@ -1539,17 +1563,18 @@ int pd_wait_host(uint64_t ticket, int n_out, void* const* out, const size_t* out
     }
     int rc = check_device_status(slot->device, err, err_cap);
     if (rc) return release(rc);
+    // a wait with unusable arguments leaves the ticket valid: the caller can wait again
     if (n_out != 0 && slot->direct_out)
-        return release(fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
-                            "the results of this call went to the arrays named at submission; wait with n_out = 0"));
+        return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap,
+                    "the results of this call went to the arrays named at submission; wait with n_out = 0");
     if (n_out != 0) {   // n_out == 0 retires the ticket without collecting anything
         if (n_out != (int)slot->out_bytes.size() || !out || !out_bytes)
-            return release(fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "the call produced %d arrays, %d were offered",
-                                (int)slot->out_bytes.size(), n_out));
+            return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "the call produced %d arrays, %d were offered",
+                        (int)slot->out_bytes.size(), n_out);
         for (int i = 0; i < n_out; ++i) {
             if (out_bytes[i] != slot->out_bytes[i] || (out_bytes[i] && !out[i]))
-                return release(fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output %d: %zu bytes offered, %zu produced", i,
-                                    out_bytes[i], slot->out_bytes[i]));
+                return fail(PD_ERR_INVALID_ARGUMENT, err, err_cap, "output %d: %zu bytes offered, %zu produced", i,
+                            out_bytes[i], slot->out_bytes[i]);
         }
         for (int i = 0; i < n_out; ++i)
             if (out_bytes[i]) memcpy(out[i], slot->host + slot->out_offset[i], out_bytes[i]);
