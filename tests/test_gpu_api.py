@@ -84,6 +84,26 @@ def test_too_many_launches_in_flight_is_an_error_and_dropped_results_free_their_
         np.testing.assert_array_equal(h.wait()[0], want[0])
 
 
+def test_native_submit_and_wait_argument_errors_keep_the_ticket():
+    from palladium_b200 import _native
+
+    n = 512
+    args = W.lotka_volterra_ensemble(n)
+    params = _native.LvRk4Params(0.01, 10)
+    ticket = _native.submit_host(0, params, 0, (n,), None, [(a.ctypes.data, a.nbytes) for a in args], [4 * n, 4 * n])
+    x, y = np.empty(n, np.float32), np.empty(n, np.float32)
+    with pytest.raises(pd.DispatchError, match="produced 2 arrays, 1 were offered"):
+        _native.wait_host(ticket, [(x.ctypes.data, x.nbytes)])
+    with pytest.raises(pd.DispatchError, match="bytes offered"):
+        _native.wait_host(ticket, [(x.ctypes.data, x.nbytes), (y.ctypes.data, 8)])
+    _native.wait_host(ticket, [(x.ctypes.data, x.nbytes), (y.ctypes.data, y.nbytes)])
+    want = oracle.lv_rk4(*args, dt=0.01, steps=10)
+    np.testing.assert_array_equal(x, want[0])
+    np.testing.assert_array_equal(y, want[1])
+    with pytest.raises(pd.DispatchError, match="unknown or already retired"):
+        _native.wait_host(ticket, [])
+
+
 def test_stepping_loop_feeds_outputs_back():
     # tests/test_dispatch_launch.py:54-72: outputs of one dispatch are the next one's inputs
     size = 64
