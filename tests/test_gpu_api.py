@@ -272,6 +272,33 @@ def test_large_host_call_is_chunked_and_still_exact():
     np.testing.assert_array_equal(got[1], want[1])
 
 
+@pytest.mark.parametrize("threads", [4, 1, 0])
+def test_pageable_inputs_of_a_large_call_go_through_the_copy_threads(threads):
+    """From 16 MB of input on, ordinary NumPy arrays are staged into page-locked buffers by the
+    library's copy threads, chunk by chunk; page-locked arrays are uploaded where they are.  Both
+    must give the oracle's result, with any number of threads (0: the driver's own pageable copy),
+    as must an eager call of that size, which fills its slot the same way."""
+    import torch
+
+    from palladium_b200 import _native
+
+    n = (1 << 20) + 4097              # 25 MB of input in 8 chunks, an odd tail
+    args = W.lotka_volterra_ensemble(n)
+    want = oracle.lv_rk4(*args, dt=0.01, steps=8)
+    locked = [torch.from_numpy(a).pin_memory().numpy() for a in args]
+    _native.set_tuning("host_copy_threads", threads)
+    try:
+        for arrays in (args, locked, args):
+            got = H.lv_solver(n, steps=8, call=pd.cuda_call_jit, math_mode=SAFE)(*arrays)
+            np.testing.assert_array_equal(got[0], want[0])
+            np.testing.assert_array_equal(got[1], want[1])
+        got = H.lv_solver(n, steps=8, math_mode=SAFE)(*args)       # eager: pd_submit_host
+        np.testing.assert_array_equal(got[0], want[0])
+        np.testing.assert_array_equal(got[1], want[1])
+    finally:
+        _native.set_tuning("host_copy_threads", 4)
+
+
 def test_chunked_gbm_keeps_global_path_indices():
     import torch
 
