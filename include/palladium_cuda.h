@@ -343,7 +343,11 @@ PD_API int pd_explain(int family, const void* params, size_t params_bytes, int m
                const int64_t grid[3], const int64_t block[3],
                pd_launch_info* info, char* err, size_t err_cap);
 
-/* Tuning knobs for experiments (e.g. "lv_items_per_thread", "vdp_variant").
+/* Tuning knobs for experiments (e.g. "lv_items_per_thread", "vdp_variant") and for
+ * the host-buffer path: "host_streams" (streams the chunks of a large call rotate
+ * over), "host_chunks", "host_copy_threads" (helper threads that stage inputs from
+ * ordinary, pageable memory into page-locked buffers for calls of 16 MB and more;
+ * 0 leaves such inputs to the driver's own pageable copy).
  * Returns PD_ERR_INVALID_ARGUMENT for an unknown key. */
 PD_API int pd_set_tuning(const char* key, int64_t value);
 PD_API int pd_get_tuning(const char* key, int64_t* value);
